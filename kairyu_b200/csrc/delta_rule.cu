@@ -1,0 +1,292 @@
+// The gated delta rule: a linear-attention mixer whose memory is one matrix S [D, V] per head and
+// request, kept in 32-bit and rewritten by every token:
+//
+//     S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
+//
+// q, k (KH heads of D) and v (H heads of V) come from a packed projection through a short causal
+// convolution over time per channel and silu; q and k are made unit vectors per head (q also times
+// D^-1/2); beta = sigmoid(b), g = exp(-exp(A_log) * softplus(a + dt_bias)) per head.  Head h uses
+// q/k head h / (H / KH).  The output is o / rms(o) * w * silu(gate) per head.
+//
+// Four kernels:
+//   delta_prepare     per token: convolution (reaching into the request's kept inputs for the taps
+//                     that lie before the step's first token), silu, unit norms, beta and g; all
+//                     results 32-bit
+//   delta_conv_state  per request: the last (taps - 1) inputs of the step become the kept inputs
+//   delta_recurrence  per (request, head, 32 columns of S): walks the request's tokens in order.
+//                     Columns of S are independent of one another, so the grid spreads them; four
+//                     lanes share a column (each holds a quarter of its D entries in registers)
+//                     and the two dot products of a token meet in two shuffles.  With a = S^T k
+//                     and b = S^T q of the OLD S:  u = beta (v - g a),  o = g b + (k.q) u,
+//                     S = g S + k u^T, which is the recurrence above with one pass over S for the
+//                     dots and one for the update
+//   delta_gated_norm  per token and head: o / sqrt(mean(o^2) + eps) * w * silu(gate)
+//
+// Every sum runs in an order that depends on the sizes alone, never on the batch or on how a
+// prompt was cut: tokens are staged in chunks of eight, but a chunk's edge changes no arithmetic.
+#include "common.cuh"
+
+#define DELTA_MAX_TAPS 16
+#define DELTA_CHUNK 8
+
+__device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
+
+// input of the convolution `back` tokens before token t (offset o within its row's portion)
+template <typename TA>
+__device__ __forceinline__ float conv_input(const TA* __restrict__ proj, int stride, const float* __restrict__ kept,
+                                            int C, int n, int t, int o, int back, int c) {
+    if (o - back >= 0) return to_float(proj[(size_t)(t - back) * stride + c]);
+    return kept[(size_t)((n - 1) + (o - back)) * C + c];
+}
+
+template <typename TA>
+__global__ void __launch_bounds__(128)
+delta_prepare_kernel(const TA* __restrict__ proj, int stride, const float* __restrict__ gates, const float* __restrict__ taps,
+                     int n, const float* __restrict__ conv_state, const int* __restrict__ row_ids,
+                     const int* __restrict__ qo_indptr, const int* __restrict__ state_slots,
+                     const float* __restrict__ A_log, const float* __restrict__ dt_bias, int KH, int D, int H, int V,
+                     float* __restrict__ qn, float* __restrict__ kn, float* __restrict__ vv, float* __restrict__ beta,
+                     float* __restrict__ decay, int num_rows, int* flag) {
+    const int t = blockIdx.x;
+    const int row = row_ids[t];
+    pdl_wait();
+    if (row < 0 || row >= num_rows) {
+        if (threadIdx.x == 0 && flag) atomicOr(flag, KB_FLAG_BAD_ROW);
+        return;
+    }
+    const int o = t - qo_indptr[row];
+    const int C = 2 * KH * D + H * V;
+    const float* kept = conv_state + (size_t)state_slots[row] * (n - 1) * C;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    // q and k heads: one warp a head
+    for (int unit = warp; unit < 2 * KH; unit += warps) {
+        float vals[8];
+        float ss = 0.0f;
+#pragma unroll
+        for (int m = 0; m < 8; ++m) {
+            const int e = lane + 32 * m;
+            float z = 0.0f;
+            if (e < D) {
+                const int c = unit * D + e;
+                for (int back = 0; back < n; ++back) z += taps[(size_t)c * n + (n - 1 - back)] * conv_input(proj, stride, kept, C, n, t, o, back, c);
+                z = silu_f(z);
+            }
+            vals[m] = z;
+            ss += z * z;
+        }
+        ss = warp_sum(ss);
+        float scale = rsqrtf(ss + 1e-6f);
+        float* dst;
+        if (unit < KH) {
+            scale *= rsqrtf((float)D);
+            dst = qn + ((size_t)t * KH + unit) * D;
+        } else {
+            dst = kn + ((size_t)t * KH + (unit - KH)) * D;
+        }
+#pragma unroll
+        for (int m = 0; m < 8; ++m) {
+            const int e = lane + 32 * m;
+            if (e < D) dst[e] = vals[m] * scale;
+        }
+    }
+    // v channels
+    for (int i = threadIdx.x; i < H * V; i += blockDim.x) {
+        const int c = 2 * KH * D + i;
+        float z = 0.0f;
+        for (int back = 0; back < n; ++back) z += taps[(size_t)c * n + (n - 1 - back)] * conv_input(proj, stride, kept, C, n, t, o, back, c);
+        vv[(size_t)t * H * V + i] = silu_f(z);
+    }
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+        const float b = gates[(size_t)t * 2 * H + h];
+        const float a = gates[(size_t)t * 2 * H + H + h] + dt_bias[h];
+        const float softplus = a > 20.0f ? a : log1pf(expf(a));
+        beta[(size_t)t * H + h] = 1.0f / (1.0f + expf(-b));
+        decay[(size_t)t * H + h] = expf(-expf(A_log[h]) * softplus);
+    }
+}
+
+template <typename TA>
+__global__ void __launch_bounds__(128)
+delta_conv_state_kernel(const TA* __restrict__ proj, int stride, float* __restrict__ conv_state, int n, int C,
+                        const int* __restrict__ qo_indptr, const int* __restrict__ state_slots) {
+    const int row = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    const int t0 = qo_indptr[row];
+    const int count = qo_indptr[row + 1] - t0;
+    float* kept = conv_state + (size_t)state_slots[row] * (n - 1) * C;
+    pdl_wait();
+    if (c >= C || count < 1) return;
+    float next[DELTA_MAX_TAPS];
+#pragma unroll
+    for (int i = 0; i < DELTA_MAX_TAPS; ++i) {
+        if (i < n - 1) {
+            const int off = count - (n - 1) + i;
+            next[i] = off >= 0 ? to_float(proj[(size_t)(t0 + off) * stride + c]) : kept[(size_t)((n - 1) + off) * C + c];
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < DELTA_MAX_TAPS; ++i)
+        if (i < n - 1) kept[(size_t)i * C + c] = next[i];
+}
+
+template <int DPT>
+__global__ void __launch_bounds__(128)
+delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ vv,
+                        const float* __restrict__ beta, const float* __restrict__ decay, float* __restrict__ states,
+                        const int* __restrict__ qo_indptr, const int* __restrict__ state_slots, int KH, int D, int H, int V,
+                        float* __restrict__ out) {
+    constexpr int LD = 4 * (DPT + 4);  // a quarter's entries lie 4 floats apart from the next quarter's: no bank conflicts
+    __shared__ __align__(16) float ks[DELTA_CHUNK][LD];
+    __shared__ __align__(16) float qs[DELTA_CHUNK][LD];
+    __shared__ float vs[DELTA_CHUNK][32];
+    __shared__ float bs[DELTA_CHUNK], gs[DELTA_CHUNK], kqs[DELTA_CHUNK];
+    const int row = blockIdx.x, h = blockIdx.y;
+    const int col0 = blockIdx.z * 32;
+    const int col = col0 + (threadIdx.x >> 2);
+    const int part = threadIdx.x & 3;
+    const int kh = h / (H / KH);
+    const int t0 = qo_indptr[row], t1 = qo_indptr[row + 1];
+    float* Sg = states + ((size_t)state_slots[row] * H + h) * D * V;
+    pdl_wait();
+    float S[DPT];
+#pragma unroll
+    for (int m = 0; m < DPT; ++m) {
+        const int i = part * DPT + m;
+        S[m] = (i < D && col < V) ? Sg[(size_t)i * V + col] : 0.0f;
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int c0 = t0; c0 < t1; c0 += DELTA_CHUNK) {
+        const int nt = min(DELTA_CHUNK, t1 - c0);
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < nt * 4 * DPT; idx += blockDim.x) {
+            const int tt = idx / (4 * DPT), i = idx % (4 * DPT);
+            const int at = (i / DPT) * (DPT + 4) + (i % DPT);
+            const size_t src = ((size_t)(c0 + tt) * KH + kh) * D + i;
+            ks[tt][at] = i < D ? kn[src] : 0.0f;
+            qs[tt][at] = i < D ? qn[src] : 0.0f;
+        }
+        for (int idx = threadIdx.x; idx < nt * 32; idx += blockDim.x) {
+            const int tt = idx >> 5, j = idx & 31;
+            vs[tt][j] = col0 + j < V ? vv[((size_t)(c0 + tt) * H + h) * V + col0 + j] : 0.0f;
+        }
+        if (threadIdx.x < nt) {
+            bs[threadIdx.x] = beta[(size_t)(c0 + threadIdx.x) * H + h];
+            gs[threadIdx.x] = decay[(size_t)(c0 + threadIdx.x) * H + h];
+        }
+        __syncthreads();
+        for (int tt = warp; tt < nt; tt += 4) {
+            float dot = 0.0f;
+            for (int i = lane; i < LD; i += 32) {
+                const bool live = (i % (DPT + 4)) < DPT;
+                if (live) dot += ks[tt][i] * qs[tt][i];
+            }
+            dot = warp_sum(dot);
+            if (lane == 0) kqs[tt] = dot;
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nt; ++tt) {
+            const float4* k4 = reinterpret_cast<const float4*>(&ks[tt][part * (DPT + 4)]);
+            const float4* q4 = reinterpret_cast<const float4*>(&qs[tt][part * (DPT + 4)]);
+            float a = 0.0f, b = 0.0f;
+#pragma unroll
+            for (int m = 0; m < DPT / 4; ++m) {
+                const float4 kv = k4[m], qv = q4[m];
+                a += S[4 * m] * kv.x; a += S[4 * m + 1] * kv.y; a += S[4 * m + 2] * kv.z; a += S[4 * m + 3] * kv.w;
+                b += S[4 * m] * qv.x; b += S[4 * m + 1] * qv.y; b += S[4 * m + 2] * qv.z; b += S[4 * m + 3] * qv.w;
+            }
+            a += __shfl_xor_sync(0xffffffffu, a, 1);
+            b += __shfl_xor_sync(0xffffffffu, b, 1);
+            a += __shfl_xor_sync(0xffffffffu, a, 2);
+            b += __shfl_xor_sync(0xffffffffu, b, 2);
+            const float g = gs[tt];
+            const float u = bs[tt] * (vs[tt][threadIdx.x >> 2] - g * a);
+#pragma unroll
+            for (int m = 0; m < DPT / 4; ++m) {
+                const float4 kv = k4[m];
+                S[4 * m] = g * S[4 * m] + kv.x * u;
+                S[4 * m + 1] = g * S[4 * m + 1] + kv.y * u;
+                S[4 * m + 2] = g * S[4 * m + 2] + kv.z * u;
+                S[4 * m + 3] = g * S[4 * m + 3] + kv.w * u;
+            }
+            if (part == 0 && col < V) out[((size_t)(c0 + tt) * H + h) * V + col] = g * b + kqs[tt] * u;
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < DPT; ++m) {
+        const int i = part * DPT + m;
+        if (i < D && col < V) Sg[(size_t)i * V + col] = S[m];
+    }
+}
+
+template <typename TA>
+__global__ void __launch_bounds__(128)
+delta_gated_norm_kernel(const float* __restrict__ o, const TA* __restrict__ proj, int stride, int gate_offset,
+                        const float* __restrict__ w, float eps, int H, int V, TA* __restrict__ out) {
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    pdl_wait();
+    for (int h = warp; h < H; h += warps) {
+        const float* oh = o + ((size_t)t * H + h) * V;
+        float ss = 0.0f;
+        for (int e = lane; e < V; e += 32) ss += oh[e] * oh[e];
+        ss = warp_sum(ss);
+        const float inv = rsqrtf(ss / (float)V + eps);
+        for (int e = lane; e < V; e += 32) {
+            const float gate = to_float(proj[(size_t)t * stride + gate_offset + h * V + e]);
+            out[(size_t)t * H * V + h * V + e] = from_float<TA>(oh[e] * inv * w[e] * silu_f(gate));
+        }
+    }
+}
+
+KB_EXPORT int kb_delta_prepare(const void* proj, int stride, int is_bf16, const float* gates, const float* taps, int n,
+                               float* conv_state, const int* row_ids, const int* qo_indptr, const int* state_slots,
+                               const float* A_log, const float* dt_bias, int KH, int D, int H, int V, float* qn, float* kn,
+                               float* vv, float* beta, float* decay, int num_rows, int T, int* flag, cudaStream_t stream) {
+    if (T == 0) return 0;
+    if (!proj || !gates || !taps || !row_ids || !qo_indptr || !state_slots || !A_log || !dt_bias || !qn || !kn || !vv || !beta || !decay)
+        return KB_ERR_NULL;
+    if (n < 1 || n > DELTA_MAX_TAPS + 1 || D < 1 || D > 256 || KH < 1 || H % KH != 0 || V < 1) return KB_ERR_UNSUPPORTED_SIZE;
+    if (n > 1 && !conv_state) return KB_ERR_NULL;
+    const int C = 2 * KH * D + H * V;
+    if (is_bf16)
+        kb_launch(delta_prepare_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, stream, (const __nv_bfloat16*)proj, stride, gates, taps, n,
+                  (const float*)conv_state, row_ids, qo_indptr, state_slots, A_log, dt_bias, KH, D, H, V, qn, kn, vv, beta, decay, num_rows, flag);
+    else
+        kb_launch(delta_prepare_kernel<float>, dim3(T), dim3(128), 0, stream, (const float*)proj, stride, gates, taps, n,
+                  (const float*)conv_state, row_ids, qo_indptr, state_slots, A_log, dt_bias, KH, D, H, V, qn, kn, vv, beta, decay, num_rows, flag);
+    int code = kb_launch_result();
+    if (code != 0 || n == 1) return code;
+    dim3 grid(num_rows, (C + 127) / 128);
+    if (is_bf16)
+        kb_launch(delta_conv_state_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, (const __nv_bfloat16*)proj, stride, conv_state, n, C, qo_indptr, state_slots);
+    else
+        kb_launch(delta_conv_state_kernel<float>, grid, dim3(128), 0, stream, (const float*)proj, stride, conv_state, n, C, qo_indptr, state_slots);
+    return kb_launch_result();
+}
+
+KB_EXPORT int kb_delta_recurrence(const float* qn, const float* kn, const float* vv, const float* beta, const float* decay,
+                                  float* states, const int* qo_indptr, const int* state_slots, int KH, int D, int H, int V,
+                                  float* out, int num_rows, cudaStream_t stream) {
+    if (num_rows == 0) return 0;
+    if (!qn || !kn || !vv || !beta || !decay || !states || !qo_indptr || !state_slots || !out) return KB_ERR_NULL;
+    if (D < 1 || D > 256 || KH < 1 || H % KH != 0 || V < 1 || H > 65535) return KB_ERR_UNSUPPORTED_SIZE;
+    dim3 grid(num_rows, H, (V + 31) / 32);
+    if (D <= 64)
+        kb_launch(delta_recurrence_kernel<16>, grid, dim3(128), 0, stream, qn, kn, vv, beta, decay, states, qo_indptr, state_slots, KH, D, H, V, out);
+    else if (D <= 128)
+        kb_launch(delta_recurrence_kernel<32>, grid, dim3(128), 0, stream, qn, kn, vv, beta, decay, states, qo_indptr, state_slots, KH, D, H, V, out);
+    else
+        kb_launch(delta_recurrence_kernel<64>, grid, dim3(128), 0, stream, qn, kn, vv, beta, decay, states, qo_indptr, state_slots, KH, D, H, V, out);
+    return kb_launch_result();
+}
+
+KB_EXPORT int kb_delta_gated_norm(const float* o, const void* proj, int stride, int gate_offset, int is_bf16, const float* w,
+                                  float eps, int H, int V, void* out, int T, cudaStream_t stream) {
+    if (T == 0) return 0;
+    if (!o || !proj || !w || !out) return KB_ERR_NULL;
+    if (is_bf16)
+        kb_launch(delta_gated_norm_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, stream, o, (const __nv_bfloat16*)proj, stride, gate_offset, w, eps, H, V, (__nv_bfloat16*)out);
+    else
+        kb_launch(delta_gated_norm_kernel<float>, dim3(T), dim3(128), 0, stream, o, (const float*)proj, stride, gate_offset, w, eps, H, V, (float*)out);
+    return kb_launch_result();
+}

@@ -1,0 +1,365 @@
+// Mixture of experts: routing, the plan of a step's (token, expert) pairs, and the two grouped
+// products of the experts.
+//
+//   moe_route     per token: the K largest of (router logits + bias) choose the experts (ties go to
+//                 the lower index); their weights are the softmax over the K chosen logits.  32-bit.
+//   moe_plan      one block: pairs p = t * K + k are counted per expert, the experts' runs are laid
+//                 side by side (`sorted` lists the pairs run by run), and the runs are cut into
+//                 tiles of MOE_TM pairs: tile -> (expert, first place in `sorted`, pairs).
+//   moe_grouped   one block per (tile, 64 output columns): a [pairs, K] x [K, 64] product with the
+//                 tile's expert's weight.  Gated form: A rows are the tokens' activations (gathered
+//                 through the pair list), the weight holds the expert's gate rows and then its up
+//                 rows, and the epilogue is the expert's activation
+//                     a = min(gate, limit), b = clamp(up, -limit, limit), y = a * sigmoid(alpha a) * (b + 1)
+//                 written at the pair's place in `sorted`.  Plain form: A rows are those y rows, and
+//                 the result goes, in 32-bit, to row p of the output, so that the K rows of a token lie
+//                 together and whoever adds them (weighted by the router) does so in the order of k.
+//                 bfloat16 runs on mma.sync m16n8k16 with 32-bit accumulators, float32 on FMAs; the
+//                 sum over K runs in ascending order in both, whatever else the tile holds.
+//   moe_combine   out[t] = sum_k weight[t, k] * rows[t * K + k]   (for callers that want plain rows)
+#include "common.cuh"
+
+#define MOE_TM 64
+#define MOE_TN 64
+#define MOE_TK 32
+#define MOE_MAX_EXPERTS 1024
+#define MOE_MAX_TOP 32
+
+template <typename TB>
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const float* __restrict__ logits, const TB* __restrict__ bias, int E, int K, int* __restrict__ ids,
+                 float* __restrict__ weights, int T) {
+    pdl_wait();
+    // one warp a token: every lane holds the logits e = lane, lane + 32, ...
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (t >= T) return;
+    float chosen_value[MOE_MAX_TOP];
+    int chosen_id[MOE_MAX_TOP];
+    float last_value = INFINITY;
+    int last_id = -1;
+    for (int k = 0; k < K; ++k) {
+        // the largest (value, then lower index) that comes after the one chosen before in that order
+        float best = -INFINITY;
+        int best_id = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float z = logits[(size_t)t * E + e] + (bias ? to_float(bias[e]) : 0.0f);
+            const bool after = z < last_value || (z == last_value && e > last_id);
+            if (after && (z > best || (z == best && e < best_id))) {
+                best = z;
+                best_id = e;
+            }
+        }
+#pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1) {
+            const float other = __shfl_xor_sync(0xffffffffu, best, offset);
+            const int other_id = __shfl_xor_sync(0xffffffffu, best_id, offset);
+            if (other > best || (other == best && other_id < best_id)) {
+                best = other;
+                best_id = other_id;
+            }
+        }
+        chosen_value[k] = best;
+        chosen_id[k] = best_id;
+        last_value = best;
+        last_id = best_id;
+    }
+    if (lane == 0) {
+        float denom = 0.0f;
+        for (int k = 0; k < K; ++k) denom += expf(chosen_value[k] - chosen_value[0]);
+        for (int k = 0; k < K; ++k) {
+            ids[(size_t)t * K + k] = chosen_id[k] < E ? chosen_id[k] : 0;
+            weights[(size_t)t * K + k] = expf(chosen_value[k] - chosen_value[0]) / denom;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(1024)
+moe_plan_kernel(const int* __restrict__ ids, int pairs, int E, int* __restrict__ sorted, int* __restrict__ tile_expert,
+                int* __restrict__ tile_first, int* __restrict__ tile_pairs, int* __restrict__ num_tiles) {
+    __shared__ int counts[MOE_MAX_EXPERTS];
+    __shared__ int cursor[MOE_MAX_EXPERTS];
+    pdl_wait();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) atomicAdd(&counts[ids[p]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0, tiles = 0;
+        for (int e = 0; e < E; ++e) {
+            cursor[e] = at;
+            for (int first = 0; first < counts[e]; first += MOE_TM) {
+                tile_expert[tiles] = e;
+                tile_first[tiles] = at + first;
+                tile_pairs[tiles] = min(MOE_TM, counts[e] - first);
+                ++tiles;
+            }
+            at += counts[e];
+        }
+        *num_tiles = tiles;
+    }
+    __syncthreads();
+    // The order of the pairs inside an expert's run is whatever the additions below give; a pair's
+    // result does not depend on its place in a tile.
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) sorted[atomicAdd(&cursor[ids[p]], 1)] = p;
+}
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+__device__ __forceinline__ float expert_activation(float gate, float up, float limit, float alpha) {
+    const float a = fminf(gate, limit);
+    const float b = fminf(fmaxf(up, -limit), limit);
+    return a * (1.0f / (1.0f + expf(-alpha * a))) * (b + 1.0f);
+}
+
+// 8 bfloat16 (or 4 float) of a row into shared memory, zeros beyond the row's end or for a row that is not there
+__device__ __forceinline__ void stage_chunk(__nv_bfloat16* dst, const __nv_bfloat16* row, int k, int Kd, bool vec) {
+    if (row && vec && k + 8 <= Kd) {
+        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(row + k);
+        return;
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) dst[e] = (row && k + e < Kd) ? row[k + e] : __float2bfloat16_rn(0.0f);
+}
+__device__ __forceinline__ void stage_chunk(float* dst, const float* row, int k, int Kd, bool vec) {
+    if (row && vec && k + 4 <= Kd) {
+        const float4 v = *reinterpret_cast<const float4*>(row + k);
+        dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
+        return;
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) dst[e] = (row && k + e < Kd) ? row[k + e] : 0.0f;
+}
+
+template <typename T> struct MoeTile;
+template <> struct MoeTile<__nv_bfloat16> { static constexpr int LD = MOE_TK + 8; static constexpr int CHUNK = 8; };
+template <> struct MoeTile<float> { static constexpr int LD = MOE_TK + 1; static constexpr int CHUNK = 4; };
+
+template <typename T, bool GATED>
+__global__ void __launch_bounds__(128)
+moe_grouped_kernel(const T* __restrict__ A, int lda, const int* __restrict__ sorted, int top, const T* __restrict__ W,
+                   int N, int Kd, const int* __restrict__ tile_expert, const int* __restrict__ tile_first,
+                   const int* __restrict__ tile_pairs, const int* __restrict__ num_tiles, float limit, float alpha,
+                   void* __restrict__ out, int vec) {
+    constexpr int LD = MoeTile<T>::LD;
+    constexpr int CHUNK = MoeTile<T>::CHUNK;
+    constexpr int NB = GATED ? 2 : 1;
+    __shared__ __align__(16) T As[MOE_TM][LD];
+    __shared__ __align__(16) T Bs[NB][MOE_TN][LD];
+    __shared__ int a_row[MOE_TM];   // source row of A per tile row, -1: none
+    __shared__ int o_row[MOE_TM];   // destination row
+    pdl_wait();
+    const int tile = blockIdx.x;
+    if (tile >= *num_tiles) return;
+    const int expert = tile_expert[tile], first = tile_first[tile], rows = tile_pairs[tile];
+    const int n0 = blockIdx.y * MOE_TN;
+    for (int i = threadIdx.x; i < MOE_TM; i += blockDim.x) {
+        int src = -1, dst = -1;
+        if (i < rows) {
+            const int p = sorted[first + i];
+            src = GATED ? p / top : first + i;
+            dst = GATED ? first + i : p;
+        }
+        a_row[i] = src;
+        o_row[i] = dst;
+    }
+    __syncthreads();
+    const size_t weight_rows = (size_t)(GATED ? 2 : 1) * N;
+    const T* We = W + (size_t)expert * weight_rows * Kd;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if constexpr (sizeof(T) == 2) {
+        const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
+        const int g = lane >> 2, tg = lane & 3;
+        float acc[NB][2][4][4];
+#pragma unroll
+        for (int b = 0; b < NB; ++b)
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) acc[b][i][j][c] = 0.0f;
+        for (int k0 = 0; k0 < Kd; k0 += MOE_TK) {
+            for (int idx = threadIdx.x; idx < MOE_TM * (MOE_TK / CHUNK); idx += blockDim.x) {
+                const int r = idx / (MOE_TK / CHUNK), c = (idx % (MOE_TK / CHUNK)) * CHUNK;
+                const int src = a_row[r];
+                stage_chunk(&As[r][c], src >= 0 ? A + (size_t)src * lda : nullptr, k0 + c, Kd, vec);
+#pragma unroll
+                for (int b = 0; b < NB; ++b) {
+                    const int n = n0 + r;
+                    stage_chunk(&Bs[b][r][c], n < N ? We + ((size_t)b * N + n) * Kd : nullptr, k0 + c, Kd, vec);
+                }
+            }
+            __syncthreads();
+#pragma unroll
+            for (int kk = 0; kk < MOE_TK; kk += 16) {
+                uint32_t a[2][4];
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const int r = wm + i * 16 + g;
+                    a[i][0] = *reinterpret_cast<const uint32_t*>(&As[r][kk + 2 * tg]);
+                    a[i][1] = *reinterpret_cast<const uint32_t*>(&As[r + 8][kk + 2 * tg]);
+                    a[i][2] = *reinterpret_cast<const uint32_t*>(&As[r][kk + 2 * tg + 8]);
+                    a[i][3] = *reinterpret_cast<const uint32_t*>(&As[r + 8][kk + 2 * tg + 8]);
+                }
+#pragma unroll
+                for (int b = 0; b < NB; ++b)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        uint32_t bf[2];
+                        const int n = wn + j * 8 + g;
+                        bf[0] = *reinterpret_cast<const uint32_t*>(&Bs[b][n][kk + 2 * tg]);
+                        bf[1] = *reinterpret_cast<const uint32_t*>(&Bs[b][n][kk + 2 * tg + 8]);
+#pragma unroll
+                        for (int i = 0; i < 2; ++i) mma_bf16_16816(acc[b][i][j], a[i], bf);
+                    }
+            }
+            __syncthreads();
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int r = wm + i * 16 + g + half * 8;
+                const int dst = o_row[r];
+                if (dst < 0) continue;
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        const int n = n0 + wn + j * 8 + 2 * tg + c;
+                        if (n >= N) continue;
+                        if constexpr (GATED)
+                            reinterpret_cast<T*>(out)[(size_t)dst * N + n] =
+                                from_float<T>(expert_activation(acc[0][i][j][half * 2 + c], acc[1][i][j][half * 2 + c], limit, alpha));
+                        else
+                            reinterpret_cast<float*>(out)[(size_t)dst * N + n] = acc[0][i][j][half * 2 + c];
+                    }
+            }
+    } else {
+        // 32-bit: thread (ty, tx) owns rows ty*4.. and columns tx, tx+8, ...
+        const int ty = threadIdx.x >> 3, tx = threadIdx.x & 7;
+        float acc[NB][4][8];
+#pragma unroll
+        for (int b = 0; b < NB; ++b)
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[b][i][j] = 0.0f;
+        for (int k0 = 0; k0 < Kd; k0 += MOE_TK) {
+            for (int idx = threadIdx.x; idx < MOE_TM * (MOE_TK / CHUNK); idx += blockDim.x) {
+                const int r = idx / (MOE_TK / CHUNK), c = (idx % (MOE_TK / CHUNK)) * CHUNK;
+                const int src = a_row[r];
+                stage_chunk(&As[r][c], src >= 0 ? A + (size_t)src * lda : nullptr, k0 + c, Kd, vec);
+#pragma unroll
+                for (int b = 0; b < NB; ++b) {
+                    const int n = n0 + r;
+                    stage_chunk(&Bs[b][r][c], n < N ? We + ((size_t)b * N + n) * Kd : nullptr, k0 + c, Kd, vec);
+                }
+            }
+            __syncthreads();
+#pragma unroll 4
+            for (int kk = 0; kk < MOE_TK; ++kk) {
+                float av[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) av[i] = As[ty * 4 + i][kk];
+#pragma unroll
+                for (int b = 0; b < NB; ++b)
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float bv = Bs[b][tx + 8 * j][kk];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) acc[b][i][j] = fmaf(av[i], bv, acc[b][i][j]);
+                    }
+            }
+            __syncthreads();
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int dst = o_row[ty * 4 + i];
+            if (dst < 0) continue;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int n = n0 + tx + 8 * j;
+                if (n >= N) continue;
+                if constexpr (GATED)
+                    reinterpret_cast<T*>(out)[(size_t)dst * N + n] = from_float<T>(expert_activation(acc[0][i][j], acc[NB - 1][i][j], limit, alpha));
+                else
+                    reinterpret_cast<float*>(out)[(size_t)dst * N + n] = acc[0][i][j];
+            }
+        }
+    }
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const float* __restrict__ rows, const float* __restrict__ weights, int K, int H, TO* __restrict__ out) {
+    pdl_wait();
+    const int t = blockIdx.x;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = 0.0f;
+        for (int k = 0; k < K; ++k) v += weights[(size_t)t * K + k] * rows[((size_t)t * K + k) * H + i];
+        out[(size_t)t * H + i] = from_float<TO>(v);
+    }
+}
+
+KB_EXPORT int kb_moe_route(const float* logits, const void* bias, int bias_is_bf16, int E, int K, int* ids, float* weights, int T,
+                           cudaStream_t stream) {
+    if (T == 0) return 0;
+    if (!logits || !ids || !weights) return KB_ERR_NULL;
+    if (E < 1 || K < 1 || K > E || K > MOE_MAX_TOP || E > MOE_MAX_EXPERTS) return KB_ERR_UNSUPPORTED_SIZE;
+    if (bias_is_bf16)
+        kb_launch(moe_route_kernel<__nv_bfloat16>, dim3((T + 3) / 4), dim3(128), 0, stream, logits, (const __nv_bfloat16*)bias, E, K, ids, weights, T);
+    else
+        kb_launch(moe_route_kernel<float>, dim3((T + 3) / 4), dim3(128), 0, stream, logits, (const float*)bias, E, K, ids, weights, T);
+    return kb_launch_result();
+}
+
+KB_EXPORT int kb_moe_max_tiles(int pairs, int E) { return (pairs + MOE_TM - 1) / MOE_TM + E; }
+
+KB_EXPORT int kb_moe_plan(const int* ids, int pairs, int E, int* sorted, int* tile_expert, int* tile_first, int* tile_pairs,
+                          int* num_tiles, cudaStream_t stream) {
+    if (pairs == 0) return 0;
+    if (!ids || !sorted || !tile_expert || !tile_first || !tile_pairs || !num_tiles) return KB_ERR_NULL;
+    if (E < 1 || E > MOE_MAX_EXPERTS) return KB_ERR_UNSUPPORTED_SIZE;
+    kb_launch(moe_plan_kernel, dim3(1), dim3(1024), 0, stream, ids, pairs, E, sorted, tile_expert, tile_first, tile_pairs, num_tiles);
+    return kb_launch_result();
+}
+
+KB_EXPORT int kb_moe_grouped(const void* A, int lda, const int* sorted, int top, const void* W, int N, int Kd, int is_bf16,
+                             int gated, const int* tile_expert, const int* tile_first, const int* tile_pairs,
+                             const int* num_tiles, int max_tiles, float limit, float alpha, void* out, cudaStream_t stream) {
+    if (max_tiles == 0) return 0;
+    if (!A || !sorted || !W || !tile_expert || !tile_first || !tile_pairs || !num_tiles || !out) return KB_ERR_NULL;
+    if (N < 1 || Kd < 1 || top < 1) return KB_ERR_BAD_ARG;
+    const int per16 = is_bf16 ? 8 : 4;
+    const int vec = (Kd % per16 == 0 && lda % per16 == 0 && ((uintptr_t)A % 16) == 0 && ((uintptr_t)W % 16) == 0) ? 1 : 0;
+    dim3 grid(max_tiles, (N + MOE_TN - 1) / MOE_TN);
+#define LAUNCH(T, G)                                                                                                          \
+    kb_launch(moe_grouped_kernel<T, G>, grid, dim3(128), 0, stream, (const T*)A, lda, sorted, top, (const T*)W, N, Kd, tile_expert, \
+              tile_first, tile_pairs, num_tiles, limit, alpha, out, vec)
+    if (is_bf16) {
+        if (gated) LAUNCH(__nv_bfloat16, true); else LAUNCH(__nv_bfloat16, false);
+    } else {
+        if (gated) LAUNCH(float, true); else LAUNCH(float, false);
+    }
+#undef LAUNCH
+    return kb_launch_result();
+}
+
+KB_EXPORT int kb_moe_combine(const float* rows, const float* weights, int K, int H, void* out, int out_is_bf16, int T,
+                             cudaStream_t stream) {
+    if (T == 0) return 0;
+    if (!rows || !weights || !out) return KB_ERR_NULL;
+    if (out_is_bf16)
+        kb_launch(moe_combine_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, rows, weights, K, H, (__nv_bfloat16*)out);
+    else
+        kb_launch(moe_combine_kernel<float>, dim3(T), dim3(256), 0, stream, rows, weights, K, H, (float*)out);
+    return kb_launch_result();
+}

@@ -1,0 +1,82 @@
+// A norm on a sub-layer's OUTPUT, with the residual sum behind it:
+//
+//     y[t]  = sum_k mix[t, k] * parts[t * K + k]          (K = 1 and no mix: y = parts)
+//     x[t] += y[t] * rsqrt(mean(y[t]^2) + eps) * w         (x: the fp32 residual stream)
+//     copy[t] = x[t] in the activation dtype               (what the next sub-layer's products read)
+//
+// The K-fold sum is how a mixture of experts hands its output over: one row per (token, chosen
+// expert) and the router's weights, added here in the order of k, so no kernel of its own
+// combines them and the order of the sum never depends on the batch.
+// Statistics, the weighted sum and the residual sum are 32-bit.  One block per token; the row
+// of y is kept in shared memory between the two passes.
+#include "common.cuh"
+
+template <typename TY, typename TW, typename TC>
+__global__ void __launch_bounds__(256)
+output_norm_add_kernel(float* __restrict__ x, const TY* __restrict__ parts, const float* __restrict__ mix,
+                       int K, const TW* __restrict__ w, TC* __restrict__ copy, int H, float eps) {
+    extern __shared__ float row[];
+    __shared__ float scratch[32];
+    pdl_wait();
+    const int t = blockIdx.x;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v;
+        if (mix) {
+            v = 0.0f;
+            for (int k = 0; k < K; ++k) v += mix[(size_t)t * K + k] * to_float(parts[((size_t)t * K + k) * H + i]);
+        } else {
+            v = to_float(parts[(size_t)t * H + i]);
+        }
+        row[i] = v;
+        ss += v * v;
+    }
+    const float total = block_sum(ss, scratch);
+    const float inv = rsqrtf(total / (float)H + eps);
+    float* xr = x + (size_t)t * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = xr[i] + row[i] * inv * to_float(w[i]);
+        xr[i] = v;
+        if (copy) copy[(size_t)t * H + i] = from_float<TC>(v);
+    }
+}
+
+template <typename TY, typename TW>
+static int launch_output_norm(float* x, const void* parts, const float* mix, int K, const void* w, void* copy,
+                              int copy_is_bf16, int T, int H, float eps, cudaStream_t stream) {
+    const size_t smem = (size_t)H * sizeof(float);
+    if (copy_is_bf16)
+        kb_launch(output_norm_add_kernel<TY, TW, __nv_bfloat16>, dim3(T), dim3(256), smem, stream, x, (const TY*)parts, mix, K,
+                  (const TW*)w, (__nv_bfloat16*)copy, H, eps);
+    else
+        kb_launch(output_norm_add_kernel<TY, TW, float>, dim3(T), dim3(256), smem, stream, x, (const TY*)parts, mix, K,
+                  (const TW*)w, (float*)copy, H, eps);
+    return kb_launch_result();
+}
+
+KB_EXPORT int kb_output_norm_add(float* x, const void* parts, int parts_is_bf16, const float* mix, int K, const void* w,
+                                 int w_is_bf16, void* copy, int copy_is_bf16, int T, int H, float eps, cudaStream_t stream) {
+    if (T == 0) return 0;
+    if (!x || !parts || !w) return KB_ERR_NULL;
+    if (H < 1 || H > 12000 || K < 1) return KB_ERR_UNSUPPORTED_SIZE;  // the row lives in 48 KB of shared memory
+    if (parts_is_bf16) {
+        if (w_is_bf16) return launch_output_norm<__nv_bfloat16, __nv_bfloat16>(x, parts, mix, K, w, copy, copy_is_bf16, T, H, eps, stream);
+        return launch_output_norm<__nv_bfloat16, float>(x, parts, mix, K, w, copy, copy_is_bf16, T, H, eps, stream);
+    }
+    if (w_is_bf16) return launch_output_norm<float, __nv_bfloat16>(x, parts, mix, K, w, copy, copy_is_bf16, T, H, eps, stream);
+    return launch_output_norm<float, float>(x, parts, mix, K, w, copy, copy_is_bf16, T, H, eps, stream);
+}
+
+// copy[t] = x[t] in bfloat16: the first sub-layer of a model reads the embedding's rows.
+__global__ void residual_copy_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ copy, size_t n) {
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) copy[i] = __float2bfloat16_rn(x[i]);
+}
+
+KB_EXPORT int kb_residual_copy(const float* x, void* copy, long long n, cudaStream_t stream) {
+    if (n == 0) return 0;
+    if (!x || !copy) return KB_ERR_NULL;
+    kb_launch(residual_copy_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, x, (__nv_bfloat16*)copy, (size_t)n);
+    return kb_launch_result();
+}

@@ -32,7 +32,7 @@ def build_parser() -> argparse.ArgumentParser:
     parser.add_argument("--out", required=True, help="folder the logits files are written to")
     parser.add_argument("--max-tokens", type=int, required=True, help="tokens the cache pool is made for")
     parser.add_argument("--page-size", type=int, default=16)
-    parser.add_argument("--max-requests", type=int, default=16, help="live requests at a time")
+    parser.add_argument("--max-requests", type=int, default=4, help="live requests at a time (state slots)")
     parser.add_argument("--decode-mode", choices=["eager", "cuda_graph"], default=None)
     parser.add_argument("--device", default="cuda")
     return parser
@@ -75,7 +75,8 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
         model,
         cache,
         storage,
-        max_model_len=model.spec.max_position_embeddings,
+        # no request outgrows the pool, and a model without positions names no shorter limit itself
+        max_model_len=min(model.spec.max_position_embeddings, max(args.max_tokens, args.page_size)),
         decode_mode=decode_mode,
         max_graph_batch=args.max_requests,
     )

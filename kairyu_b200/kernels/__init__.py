@@ -287,8 +287,8 @@ def paged_attention_generic(
         raise KernelError("paged_attention_generic: dtype or cache shape mismatch")
     if q.stride(1) != 1 or out.stride(1) != 1 or not k_cache.is_contiguous() or not v_cache.is_contiguous():
         raise KernelError("paged_attention_generic: inner strides must be 1 and caches contiguous")
-    if head_dim > 256:
-        raise KernelError(f"paged_attention_generic: head_dim {head_dim} > 256 is not supported")
+    if head_dim > 512:
+        raise KernelError(f"paged_attention_generic: head_dim {head_dim} > 512 is not supported")
     if num_q_heads % num_kv_heads:
         raise KernelError("paged_attention_generic: query heads must be a multiple of KV heads")
     T = q.shape[0]
@@ -1118,3 +1118,296 @@ __all__ = [
     "skinny_blocks",
     "swiglu",
 ]
+
+
+# ----------------------------------------------------------------------------- norm on a sub-layer's output
+
+
+@dataclass
+class ResidualCopy:
+    """What a block that norms its sub-layers' OUTPUTS hands to the block after it: the residual's
+    rows in the activation dtype (the sub-layers read the stream itself, so the next one wants them
+    as product operands).  Nothing is left to add: ``pending_delta`` is None."""
+
+    values: torch.Tensor
+    pending_delta = None
+
+
+@dataclass
+class WeightedRows:
+    """A sub-layer's output as K rows a token and their weights (a mixture of experts before the
+    sum): ``rows`` [tokens * K, width] fp32, ``weights`` [tokens, K] fp32."""
+
+    rows: torch.Tensor
+    weights: torch.Tensor
+
+
+def output_norm_add(residual: torch.Tensor, y, weight: torch.Tensor, eps: float, copy: Optional[torch.Tensor]) -> None:
+    """``residual += rmsnorm(y) * weight`` and ``copy = residual`` in the activation dtype (when given).
+    ``y``: rows of the residual's shape, or a :class:`WeightedRows` whose K rows a token are summed
+    first, weighted, in the order of k."""
+    mix = None
+    K = 1
+    rows = y
+    if isinstance(y, WeightedRows):
+        rows, mix = y.rows, y.weights
+        K = mix.shape[1]
+        if mix.dtype != torch.float32 or not mix.is_contiguous() or mix.shape[0] != residual.shape[0]:
+            raise KernelError("output_norm_add: the weights of weighted rows must be contiguous fp32 [tokens, K]")
+    _need_cuda("output_norm_add", residual, rows, weight, copy, mix)
+    T, H = residual.shape
+    if residual.dtype != torch.float32 or not residual.is_contiguous() or not rows.is_contiguous() or rows.shape != (T * K, H):
+        raise KernelError("output_norm_add: the residual must be contiguous fp32 and the rows of its width")
+    if weight.numel() != H or (copy is not None and (copy.shape != (T, H) or not copy.is_contiguous())):
+        raise KernelError("output_norm_add: shape mismatch")
+    fn = _fn("sublayer_norm", "kb_output_norm_add", [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
+    _check(
+        fn(residual.data_ptr(), rows.data_ptr(), _is_bf16(rows, "output_norm_add"), _ptr(mix), K, weight.data_ptr(),
+           _is_bf16(weight, "output_norm_add"), _ptr(copy), _is_bf16(copy, "output_norm_add") if copy is not None else 0, T, H,
+           float(eps), _stream()),
+        "output_norm_add",
+    )
+
+
+def residual_copy(residual: torch.Tensor, copy: torch.Tensor) -> None:
+    """copy = residual in bfloat16."""
+    _need_cuda("residual_copy", residual, copy)
+    if residual.dtype != torch.float32 or copy.dtype != torch.bfloat16 or residual.shape != copy.shape or not (residual.is_contiguous() and copy.is_contiguous()):
+        raise KernelError("residual_copy: needs a contiguous fp32 source and a bfloat16 copy of its shape")
+    fn = _fn("sublayer_norm", "kb_residual_copy", [c_void_p, c_void_p, ctypes.c_longlong, c_void_p])
+    _check(fn(residual.data_ptr(), copy.data_ptr(), residual.numel(), _stream()), "residual_copy")
+
+
+# ----------------------------------------------------------------------------- latent attention
+
+
+def latent_norm_write(
+    packed: torch.Tensor,
+    offset: int,
+    rank: int,
+    weight: torch.Tensor,
+    eps: float,
+    cache: torch.Tensor,
+    *,
+    positions: torch.Tensor,
+    row_ids: torch.Tensor,
+    block_table: torch.Tensor,
+    write_from: Optional[torch.Tensor],
+    flag: Optional[torch.Tensor] = None,
+) -> None:
+    """Columns [offset, offset + rank) of every row of ``packed`` are RMS-normed (32-bit) and written,
+    in the cache's dtype, at the token's place in its request's pages.  ``cache``: [pages, page_size, 1, rank]."""
+    _need_cuda("latent_norm_write", packed, weight, cache, positions, row_ids, block_table, write_from, flag)
+    _need_i32("latent_norm_write", positions, row_ids, block_table, write_from)
+    num_pages, page_size, heads, width = cache.shape
+    if heads != 1 or width != rank or not cache.is_contiguous() or cache.dtype != packed.dtype:
+        raise KernelError("latent_norm_write: the cache must be contiguous [pages, page_size, 1, rank] in the activations' dtype")
+    if packed.stride(1) != 1 or offset < 0 or offset + rank > packed.shape[1] or weight.numel() != rank:
+        raise KernelError("latent_norm_write: the packed rows do not hold the latent's columns")
+    fn = _fn("latent_cache", "kb_latent_norm_write",
+             [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+              c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(
+        fn(packed.data_ptr(), packed.stride(0), int(offset), int(rank), _is_bf16(packed, "latent_norm_write"), weight.data_ptr(),
+           _is_bf16(weight, "latent_norm_write"), float(eps), positions.data_ptr(), row_ids.data_ptr(), block_table.data_ptr(),
+           block_table.shape[1], _ptr(write_from), cache.data_ptr(), page_size, num_pages, block_table.shape[0], packed.shape[0],
+           _ptr(flag), _stream()),
+        "latent_norm_write",
+    )
+
+
+def heads_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
+    """A product per head: ``out[t, h, :] = weight[h] @ x[t, h, :]``.  ``x`` [tokens, heads, K] and
+    ``out`` [tokens, heads, N] may be views with any row stride (inner stride 1); ``weight`` is
+    contiguous [heads, N, K].  bfloat16: the library's batched product (fp32 accumulation);
+    float32: this package's FMA product, one launch a head."""
+    _need_cuda("heads_linear", x, weight, out)
+    T, H, K = x.shape
+    N = weight.shape[1]
+    if weight.shape != (H, N, K) or out.shape != (T, H, N) or not weight.is_contiguous():
+        raise KernelError(f"heads_linear: shapes x{tuple(x.shape)} w{tuple(weight.shape)} out{tuple(out.shape)} do not agree")
+    if x.stride(2) != 1 or out.stride(2) != 1 or x.stride(1) != K or out.stride(1) != N:
+        raise KernelError("heads_linear: a token's heads must lie side by side")
+    if T == 0:
+        return
+    if x.dtype == torch.float32:
+        if weight.dtype != torch.float32 or out.dtype != torch.float32:
+            raise KernelError("heads_linear: the 32-bit path needs fp32 weights and output")
+        fn = _fn("gemm_f32", "kb_gemm_f32", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+        for h in range(H):
+            _check(fn(x.data_ptr() + 4 * h * K, x.stride(0), weight.data_ptr() + 4 * h * N * K, K, None, out.data_ptr() + 4 * h * N,
+                      out.stride(0), T, N, K, _stream()), "heads_linear")
+        return
+    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("heads_linear: bfloat16 or float32 throughout")
+    torch.bmm(x.transpose(0, 1), weight.transpose(1, 2), out=out.transpose(0, 1))
+
+
+# ----------------------------------------------------------------------------- gated delta rule
+
+
+def delta_prepare(
+    packed: torch.Tensor,
+    gates: torch.Tensor,
+    taps: torch.Tensor,
+    conv_state: Optional[torch.Tensor],
+    *,
+    row_ids: torch.Tensor,
+    qo_indptr: torch.Tensor,
+    state_slots: torch.Tensor,
+    a_log: torch.Tensor,
+    dt_bias: torch.Tensor,
+    kv_heads: int,
+    dim: int,
+    heads: int,
+    vdim: int,
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    beta: torch.Tensor,
+    decay: torch.Tensor,
+    flag: Optional[torch.Tensor] = None,
+) -> None:
+    """Convolution + silu of the packed q|k|v columns, unit norms of q and k, beta and the decay, all
+    to fp32; then the step's last inputs become the requests' kept inputs (``conv_state``
+    [slots, taps - 1, channels] fp32)."""
+    _need_cuda("delta_prepare", packed, gates, taps, conv_state, row_ids, qo_indptr, state_slots, a_log, dt_bias, q, k, v, beta, decay, flag)
+    _need_i32("delta_prepare", row_ids, qo_indptr, state_slots)
+    T = packed.shape[0]
+    channels = 2 * kv_heads * dim + heads * vdim
+    n = taps.shape[1]
+    for tensor in (gates, taps, a_log, dt_bias, q, k, v, beta, decay) + ((conv_state,) if conv_state is not None else ()):
+        if tensor.dtype != torch.float32 or not tensor.is_contiguous():
+            raise KernelError("delta_prepare: everything but the packed projection is contiguous fp32")
+    if packed.stride(1) != 1 or packed.shape[1] < channels or taps.shape[0] != channels or gates.shape != (T, 2 * heads):
+        raise KernelError("delta_prepare: the packed projection, the taps or the gates do not fit the sizes")
+    if conv_state is not None and tuple(conv_state.shape[1:]) != (n - 1, channels):
+        raise KernelError("delta_prepare: the kept inputs must be [slots, taps - 1, channels]")
+    if q.numel() != T * kv_heads * dim or k.numel() != q.numel() or v.numel() != T * heads * vdim or beta.numel() != T * heads or decay.numel() != T * heads:
+        raise KernelError("delta_prepare: an output does not fit")
+    fn = _fn("delta_rule", "kb_delta_prepare",
+             [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+              c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p])
+    _check(
+        fn(packed.data_ptr(), packed.stride(0), _is_bf16(packed, "delta_prepare"), gates.data_ptr(), taps.data_ptr(), n, _ptr(conv_state),
+           row_ids.data_ptr(), qo_indptr.data_ptr(), state_slots.data_ptr(), a_log.data_ptr(), dt_bias.data_ptr(), kv_heads, dim, heads,
+           vdim, q.data_ptr(), k.data_ptr(), v.data_ptr(), beta.data_ptr(), decay.data_ptr(), qo_indptr.numel() - 1, T, _ptr(flag), _stream()),
+        "delta_prepare",
+        launches=2 if n > 1 else 1,
+    )
+
+
+def delta_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Tensor, decay: torch.Tensor, states: torch.Tensor,
+                     out: torch.Tensor, *, qo_indptr: torch.Tensor, state_slots: torch.Tensor, kv_heads: int, dim: int, heads: int,
+                     vdim: int) -> None:
+    """Every row's tokens in order through S <- g S + k (beta (v - g S^T k))^T, o = S^T q; ``states``
+    [slots, heads, dim, vdim] fp32 is read and left updated."""
+    _need_cuda("delta_recurrence", q, k, v, beta, decay, states, out, qo_indptr, state_slots)
+    _need_i32("delta_recurrence", qo_indptr, state_slots)
+    for tensor in (q, k, v, beta, decay, states, out):
+        if tensor.dtype != torch.float32 or not tensor.is_contiguous():
+            raise KernelError("delta_recurrence: contiguous fp32 tensors only")
+    if tuple(states.shape[1:]) != (heads, dim, vdim) or out.numel() != v.numel():
+        raise KernelError("delta_recurrence: the state must be [slots, heads, dim, vdim] and the output as large as v")
+    if dim > 256:
+        raise KernelError(f"delta_recurrence: dim {dim} > 256 is not supported")
+    fn = _fn("delta_rule", "kb_delta_recurrence",
+             [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p])
+    _check(
+        fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), beta.data_ptr(), decay.data_ptr(), states.data_ptr(), qo_indptr.data_ptr(),
+           state_slots.data_ptr(), kv_heads, dim, heads, vdim, out.data_ptr(), qo_indptr.numel() - 1, _stream()),
+        "delta_recurrence",
+    )
+
+
+def delta_gated_norm(o: torch.Tensor, packed: torch.Tensor, gate_offset: int, weight: torch.Tensor, eps: float, out: torch.Tensor, *,
+                     heads: int, vdim: int) -> None:
+    """out[t, h] = o[t, h] / rms(o[t, h]) * weight * silu(gate[t, h]); the gate is columns
+    [gate_offset, gate_offset + heads * vdim) of the packed projection."""
+    _need_cuda("delta_gated_norm", o, packed, weight, out)
+    T = packed.shape[0]
+    if o.dtype != torch.float32 or weight.dtype != torch.float32 or not o.is_contiguous() or not out.is_contiguous() or out.dtype != packed.dtype:
+        raise KernelError("delta_gated_norm: o and the weight are fp32, the output has the projection's dtype")
+    if out.shape != (T, heads * vdim) or o.numel() != T * heads * vdim or weight.numel() != vdim or gate_offset + heads * vdim > packed.shape[1] or packed.stride(1) != 1:
+        raise KernelError("delta_gated_norm: shape mismatch")
+    fn = _fn("delta_rule", "kb_delta_gated_norm", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_float, c_int, c_int, c_void_p, c_int, c_void_p])
+    _check(fn(o.data_ptr(), packed.data_ptr(), packed.stride(0), int(gate_offset), _is_bf16(packed, "delta_gated_norm"), weight.data_ptr(),
+              float(eps), heads, vdim, out.data_ptr(), T, _stream()), "delta_gated_norm")
+
+
+# ----------------------------------------------------------------------------- mixture of experts
+
+
+def moe_max_tiles(pairs: int, experts: int) -> int:
+    """Upper bound of the tiles ``moe_plan`` cuts ``pairs`` (token, expert) pairs into (csrc/moe.cu: MOE_TM = 64)."""
+    return -(-pairs // 64) + experts
+
+
+def moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], top: int, ids: torch.Tensor, weights: torch.Tensor) -> None:
+    """The ``top`` largest of logits + bias per token and the softmax over them (fp32)."""
+    _need_cuda("moe_route", logits, bias, ids, weights)
+    T, E = logits.shape
+    if logits.dtype != torch.float32 or not logits.is_contiguous() or weights.dtype != torch.float32 or ids.dtype != torch.int32:
+        raise KernelError("moe_route: fp32 logits and weights, int32 ids")
+    if ids.shape != (T, top) or weights.shape != (T, top) or not ids.is_contiguous() or not weights.is_contiguous():
+        raise KernelError("moe_route: ids and weights must be contiguous [tokens, top]")
+    if bias is not None and (bias.numel() != E or not bias.is_contiguous()):
+        raise KernelError("moe_route: the bias must have one entry an expert")
+    fn = _fn("moe", "kb_moe_route", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p])
+    _check(fn(logits.data_ptr(), _ptr(bias), _is_bf16(bias, "moe_route") if bias is not None else 0, E, int(top), ids.data_ptr(),
+              weights.data_ptr(), T, _stream()), "moe_route")
+
+
+def moe_plan(ids: torch.Tensor, experts: int, plan: torch.Tensor) -> dict:
+    """Sort a step's (token, expert) pairs by expert and cut the runs into tiles.  ``plan``: int32
+    scratch of at least ``pairs + 3 * moe_max_tiles + 1`` entries; returns views into it."""
+    _need_cuda("moe_plan", ids, plan)
+    _need_i32("moe_plan", ids, plan)
+    pairs = ids.numel()
+    tiles = moe_max_tiles(pairs, experts)
+    if plan.numel() < pairs + 3 * tiles + 1:
+        raise KernelError("moe_plan: the scratch is too small")
+    views = {
+        "sorted": plan[:pairs],
+        "tile_expert": plan[pairs : pairs + tiles],
+        "tile_first": plan[pairs + tiles : pairs + 2 * tiles],
+        "tile_pairs": plan[pairs + 2 * tiles : pairs + 3 * tiles],
+        "num_tiles": plan[pairs + 3 * tiles : pairs + 3 * tiles + 1],
+        "max_tiles": tiles,
+    }
+    fn = _fn("moe", "kb_moe_plan", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(fn(ids.data_ptr(), pairs, int(experts), views["sorted"].data_ptr(), views["tile_expert"].data_ptr(), views["tile_first"].data_ptr(),
+              views["tile_pairs"].data_ptr(), views["num_tiles"].data_ptr(), _stream()), "moe_plan")
+    return views
+
+
+def moe_grouped(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, plan: dict, *, top: int, gated: bool, limit: float = 0.0,
+                alpha: float = 1.702) -> None:
+    """The experts' products over a planned step.  ``gated``: ``a`` [tokens, K] activations, ``weight``
+    [experts, 2 * N, K] (gate rows, then up rows), ``out`` [pairs, N] in the activations' dtype, rows
+    in the plan's sorted order, after the experts' activation.  Otherwise ``a`` is such an ``out``,
+    ``weight`` [experts, N, K] and ``out`` fp32 [pairs, N] with row t * top + k for token t's k-th expert."""
+    _need_cuda("moe_grouped", a, weight, out)
+    experts, rows, K = weight.shape
+    N = rows // 2 if gated else rows
+    pairs = plan["sorted"].numel()
+    if a.dtype != weight.dtype or a.shape[1] != K or a.stride(1) != 1 or not weight.is_contiguous() or not out.is_contiguous():
+        raise KernelError("moe_grouped: operands must share a dtype and K, the weight and the output be contiguous")
+    if out.shape != (pairs, N) or out.dtype != (a.dtype if gated else torch.float32):
+        raise KernelError("moe_grouped: the output does not fit")
+    fn = _fn("moe", "kb_moe_grouped", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                        c_void_p, c_int, c_float, c_float, c_void_p, c_void_p])
+    _check(fn(a.data_ptr(), a.stride(0), plan["sorted"].data_ptr(), int(top), weight.data_ptr(), N, K, _is_bf16(a, "moe_grouped"), 1 if gated else 0,
+              plan["tile_expert"].data_ptr(), plan["tile_first"].data_ptr(), plan["tile_pairs"].data_ptr(), plan["num_tiles"].data_ptr(),
+              plan["max_tiles"], float(limit), float(alpha), out.data_ptr(), _stream()), "moe_grouped")
+
+
+def moe_combine(rows: torch.Tensor, weights: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t] = sum_k weights[t, k] * rows[t * K + k] (fp32 sum, in the order of k)."""
+    _need_cuda("moe_combine", rows, weights, out)
+    T, K = weights.shape
+    H = rows.shape[1]
+    if rows.dtype != torch.float32 or weights.dtype != torch.float32 or rows.shape[0] != T * K or out.shape != (T, H) or not (rows.is_contiguous() and weights.is_contiguous() and out.is_contiguous()):
+        raise KernelError("moe_combine: shape or dtype mismatch")
+    fn = _fn("moe", "kb_moe_combine", [c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p])
+    _check(fn(rows.data_ptr(), weights.data_ptr(), K, H, out.data_ptr(), _is_bf16(out, "moe_combine"), T, _stream()), "moe_combine")

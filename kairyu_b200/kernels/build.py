@@ -39,6 +39,10 @@ LIBRARIES: dict[str, list[str]] = {
     "gemm_skinny": [],
     "gemm_tc5": [],
     "sampling": [],
+    "sublayer_norm": [],
+    "latent_cache": [],
+    "delta_rule": [],
+    "moe": [],
 }
 
 _lock = threading.Lock()

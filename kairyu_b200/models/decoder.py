@@ -123,5 +123,7 @@ class DecoderModel:
                 residual, delta = block.forward(residual, delta, ctx, view)
         if want_rows is None or want_rows.numel() == 0:
             return None
+        # a block may hand on something other than a sum still to be added; it says what is left to add
+        delta = getattr(delta, "pending_delta", delta)
         hidden = self.final_norm.apply(residual, delta, ctx, rows=want_rows)
         return self.head.forward(hidden, ctx)

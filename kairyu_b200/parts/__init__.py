@@ -1,7 +1,7 @@
 """Model parts and their registries.  Importing this package registers the
 built-in parts; more can be registered from outside with the same decorators."""
 
-from kairyu_b200.parts import attention, block, embedding, ffn, norm, rope  # noqa: F401  (registration)
+from kairyu_b200.parts import attention, block, delta_rule, embedding, ffn, latent_attention, moe, norm, rope  # noqa: F401  (registration)
 from kairyu_b200.parts.base import (
     BLOCKS,
     EMBEDDINGS,

@@ -53,9 +53,9 @@ class LayerSpec:
     prefix: str  # tensor-name prefix, e.g. "model.layers.3"
     block: str
     mixer: PartSpec
-    ffn: PartSpec
+    ffn: Optional[PartSpec]  # None: a layer without a feed-forward (for arrangements that take one)
     mixer_norm: PartSpec
-    ffn_norm: PartSpec
+    ffn_norm: Optional[PartSpec]
 
 
 @dataclass(frozen=True)
@@ -117,7 +117,8 @@ class PagedKVSpec:
     """Keys and values in pages: ``window=None`` keeps every key, an integer
     keeps the last ``window`` positions (older pages go back to the pool).
     ``v_head_dim``: the width of a value row where it differs from a key row's
-    (a mixer whose values are narrower than its keys; None: the same).  Slots
+    (a mixer whose values are narrower than its keys; None: the same; 0: no value
+    rows at all, for a mixer whose keys and values are products of one cached row).  Slots
     whose specs are equal share a group: pages of one geometry, one block table."""
 
     num_kv_heads: int

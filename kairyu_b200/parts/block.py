@@ -89,3 +89,59 @@ class PreNormBlock(Block):
         mixed = self.mixer.forward(normed, ctx, cache, fold=self.ffn_norm.fold_target(residual, ctx, "ffn"))
         fold = next_norm.fold_target(residual, ctx, "mixer") if next_norm is not None else None
         return residual, self.ffn.forward(mixed, ctx, fold=fold)
+
+
+@BLOCKS.register("output_norm")
+class OutputNormBlock(Block):
+    """``x += norm1(mixer(x)); x += norm2(ffn(x))``: the norms sit on the sub-layers' outputs, and the
+    sub-layers read the stream itself.  A layer may have no feed-forward.
+
+    The residual is fp32; one kernel per sub-layer norms the output, adds it to the residual and
+    leaves the residual's rows in the activation dtype for the next products (``Norm.add_normed``).
+    That copy travels to the next block in place of a pending delta (``kernels.ResidualCopy``).  A
+    feed-forward that can hand over its rows before their weighted sum (a mixture of experts) does,
+    and the same kernel adds them.
+    """
+
+    graph_safe = True
+
+    def __init__(self, *, layer: LayerSpec, dtype: torch.dtype, device: str, shared: dict, **_: object) -> None:
+        context = dict(dtype=dtype, device=device, shared=shared)
+        self.dtype = dtype
+        self.mixer = MIXERS.build(layer.mixer, **context)
+        self.mixer_norm = NORMS.build(layer.mixer_norm, **context)
+        self.ffn = FEED_FORWARDS.build(layer.ffn, **context) if layer.ffn is not None else None
+        self.ffn_norm = NORMS.build(layer.ffn_norm, **context) if layer.ffn is not None else None
+        self._parts = tuple(part for part in (self.mixer, self.mixer_norm, self.ffn, self.ffn_norm) if part is not None)
+        for norm in (self.mixer_norm, self.ffn_norm):
+            if norm is not None and not hasattr(norm, "add_normed"):
+                raise ValueError("this arrangement needs norms that offer add_normed (rmsnorm does)")
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        return [spec for part in self._parts for spec in part.tensor_specs()]
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        for part in self._parts:
+            part.load(tensors)
+
+    def bytes_streamed(self) -> int:
+        return sum(part.bytes_streamed() for part in self._parts)
+
+    def forward(self, residual: torch.Tensor, delta, ctx: StepContext, cache: CacheView):
+        if isinstance(delta, kernels.ResidualCopy):
+            rows = delta.values
+        elif delta is not None:
+            raise ValueError("an output-norm block cannot follow a block that leaves a sum to be added")
+        elif self.dtype == torch.float32:
+            rows = residual
+        else:  # the model's first block: the embedding's rows
+            rows = ctx.workspace.buffer("residual.copy", residual.shape[0], residual.shape[1], self.dtype)
+            kernels.residual_copy(residual, rows)
+        rows = self.mixer_norm.add_normed(residual, self.mixer.forward(rows, ctx, cache), ctx)
+        if self.ffn is not None:
+            if getattr(self.ffn, "weighted_rows", False):
+                output = self.ffn.forward(rows, ctx, combine=False)
+            else:
+                output = self.ffn.forward(rows, ctx)
+            rows = self.ffn_norm.add_normed(residual, output, ctx)
+        return residual, (None if rows is residual else kernels.ResidualCopy(rows))

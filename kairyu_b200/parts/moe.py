@@ -1,0 +1,112 @@
+"""Mixture of experts as a feed-forward: every token runs ``top`` of ``num_experts`` small gated
+feed-forward layers and adds their outputs, weighted.
+
+Routing: logits ``W_router x + bias`` in 32-bit; the ``top`` largest choose (ties: the lower index);
+the weights are the softmax over the chosen logits only.  An expert is
+``W_down(a * sigmoid(alpha a) * (b + 1))`` with ``a = min(W_gate x, limit)`` and
+``b = clamp(W_up x, -limit, limit)``.
+
+A step's (token, expert) pairs are sorted by expert on the device and cut into tiles; one grouped
+product runs gate and up with the activation in its epilogue, a second runs down
+(``csrc/moe.cu``).  Nothing comes back to the host, so the work can sit in a captured graph.  The
+down product leaves one fp32 row per pair; ``forward(..., combine=False)`` hands those and the
+router's weights on (``kernels.WeightedRows``) for a kernel that adds them on its way, otherwise
+they are added here.
+"""
+
+from __future__ import annotations
+
+from typing import Mapping, Optional
+
+import torch
+
+from kairyu_b200 import kernels
+from kairyu_b200.parts.base import FEED_FORWARDS, FeedForward, StepContext, TensorSpec
+
+
+@FEED_FORWARDS.register("moe")
+class MixtureOfExperts(FeedForward):
+    graph_safe = True
+    weighted_rows = True  # forward takes combine=False
+
+    def __init__(
+        self,
+        *,
+        prefix: str,
+        hidden_size: int,
+        intermediate_size: int,
+        num_experts: int,
+        top: int,
+        limit: float,
+        alpha: float = 1.702,
+        router_bias: bool = True,
+        dtype: torch.dtype,
+        device: str,
+        **_: object,
+    ) -> None:
+        if not 1 <= top <= num_experts:
+            raise ValueError(f"a token cannot use {top} of {num_experts} experts")
+        self.prefix = prefix
+        self.hidden_size = hidden_size
+        self.intermediate_size = intermediate_size
+        self.num_experts = num_experts
+        self.top = top
+        self.limit = float(limit)
+        self.alpha = float(alpha)
+        self.router_bias = router_bias
+        self.dtype = dtype
+        self.w_router: Optional[torch.Tensor] = None
+        self.b_router: Optional[torch.Tensor] = None
+        self.w_gate_up: Optional[torch.Tensor] = None  # [experts, 2 * intermediate, hidden]: gate rows, then up rows
+        self.w_down: Optional[torch.Tensor] = None     # [experts, hidden, intermediate]
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        p, h, f = self.prefix, self.hidden_size, self.intermediate_size
+        specs = []
+        for e in range(self.num_experts):
+            specs += [
+                TensorSpec(f"{p}.e{e}.gate", (f, h)),
+                TensorSpec(f"{p}.e{e}.up", (f, h)),
+                TensorSpec(f"{p}.e{e}.down", (h, f)),
+            ]
+        specs.append(TensorSpec(f"{p}.router", (self.num_experts, h)))
+        if self.router_bias:
+            specs.append(TensorSpec(f"{p}.router.b", (self.num_experts,), role="vector", init="normal"))
+        return specs
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        p = self.prefix
+        experts = range(self.num_experts)
+        self.w_gate_up = torch.stack(
+            [torch.cat([tensors[f"{p}.e{e}.gate"], tensors[f"{p}.e{e}.up"]], dim=0) for e in experts], dim=0
+        ).contiguous()
+        self.w_down = torch.stack([tensors[f"{p}.e{e}.down"] for e in experts], dim=0).contiguous()
+        self.w_router = tensors[f"{p}.router"].contiguous()
+        self.b_router = tensors[f"{p}.router.b"].contiguous() if self.router_bias else None
+
+    def bytes_streamed(self) -> int:
+        """What a single token reads: the router and ``top`` experts."""
+        per_expert = (self.w_gate_up[0].numel() + self.w_down[0].numel()) * self.w_down.element_size()
+        return self.w_router.numel() * self.w_router.element_size() + self.top * per_expert
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, combine: bool = True):
+        tokens = x.shape[0]
+        ws = ctx.workspace
+        experts, top = self.num_experts, self.top
+        logits = ws.buffer("moe.logits", tokens, experts, torch.float32)
+        kernels.linear(x, self.w_router, None, logits)
+        ids = ws.buffer("moe.ids", tokens, top, torch.int32)
+        weights = ws.buffer("moe.weights", tokens, top, torch.float32)
+        kernels.moe_route(logits, self.b_router, top, ids, weights)
+        pairs = tokens * top
+        scratch = ws.flat("moe.plan", pairs + 3 * kernels.moe_max_tiles(pairs, experts) + 1, torch.int32)
+        plan = kernels.moe_plan(ids.view(-1), experts, scratch)
+        hidden = ws.buffer("moe.hidden", pairs, self.intermediate_size, self.dtype)
+        kernels.moe_grouped(x, self.w_gate_up, hidden, plan, top=top, gated=True, limit=self.limit, alpha=self.alpha)
+        rows = ws.buffer("moe.rows", pairs, self.hidden_size, torch.float32)
+        kernels.moe_grouped(hidden, self.w_down, rows, plan, top=top, gated=False)
+        if not combine:
+            return kernels.WeightedRows(rows, weights)
+        out = ws.buffer("moe.out", tokens, self.hidden_size, self.dtype)
+        kernels.moe_combine(rows, weights, out)
+        return out

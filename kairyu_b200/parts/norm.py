@@ -47,6 +47,17 @@ class RMSNorm(Norm):
         kernels.rmsnorm(residual, self.weight, self.eps, out, delta=delta, rows=rows)
         return out
 
+    def add_normed(self, residual: torch.Tensor, y, ctx: StepContext) -> torch.Tensor:
+        """For an arrangement that norms a sub-layer's OUTPUT: ``residual += norm(y)``.  Returns the
+        residual's rows as the next sub-layer's products read them: the fp32 residual itself in
+        32-bit mode, else a copy in the activation dtype that the same kernel writes.  ``y`` may be a
+        ``kernels.WeightedRows`` (a mixture's rows before their weighted sum)."""
+        copy = None
+        if self.dtype != torch.float32:
+            copy = ctx.workspace.buffer("residual.copy", residual.shape[0], self.size, self.dtype)
+        kernels.output_norm_add(residual, y, self.weight, self.eps, copy)
+        return residual if copy is None else copy
+
     def fold_target(self, residual: torch.Tensor, ctx: StepContext, tag: str) -> "kernels.ResidualNorm":
         """For a product that takes this norm's first half into its epilogue: it adds its result
         to ``residual`` and leaves the rows weighted and their sums of squares; the product that

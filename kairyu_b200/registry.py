@@ -44,8 +44,9 @@ def supported_architectures() -> tuple[str, ...]:
 
 
 def architecture_of(config: Mapping[str, Any]) -> Architecture:
+    # HF-style files list names under "architectures"; a file may also name its one design under "architecture"
     names = config.get("architectures") or []
-    name = names[0] if names else ""
+    name = names[0] if names else config.get("architecture") or ""
     if name not in _ARCHITECTURES:
         raise ConfigError(
             f"unsupported architecture {name!r}; supported: {', '.join(supported_architectures())}"
@@ -58,6 +59,9 @@ def _register_builtin() -> None:
 
     register_architecture("LlamaForCausalLM", llama.parse_llama, llama.llama_spec)
     register_architecture("Qwen3ForCausalLM", llama.parse_qwen3, llama.qwen3_spec)
+    from kairyu_b200.models import makilorn
+
+    register_architecture("Makilorn", makilorn.parse_makilorn, makilorn.makilorn_spec)
 
 
 _register_builtin()

@@ -4,7 +4,7 @@ model folder (config.json + model.safetensors) that the loader reads back.
 Tensors are drawn in the order the model lists them, each from its own
 generator seeded by (seed, position in that order), so a seed fixes every
 tensor whatever the others' sizes.  Matrices and biases ~N(0, 0.02); norm
-weights 1 + N(0, 0.1).
+weights 1 + N(0, 0.1); the taps of a short convolution ~N(0, 0.5).
 """
 
 from __future__ import annotations
@@ -31,6 +31,8 @@ def _draw(spec: TensorSpec, seed: int, index: int, device: str) -> torch.Tensor:
         return 1.0 + 0.1 * values
     if spec.init == "normal":
         return 0.02 * values
+    if spec.init == "taps":  # the few weights of a short convolution: of the order of one
+        return 0.5 * values
     raise ValueError(f"unknown init {spec.init!r} for {spec.name}")
 
 
