@@ -1,0 +1,228 @@
+"""Makilorn on the GPU against the plain implementation in ``makilorn_plain.py``: every mechanism
+alone, whole prompts against token-by-token decoding, portions down to two tokens, unequal
+requests in one batch over a pool so small that pages and state slots are used again, windows'
+edges, long decoding, and greedy generation through ``LLM.generate``."""
+
+import json
+
+import numpy as np
+import pytest
+import torch
+
+import makilorn_plain as plain
+import traces
+from makilorn_cases import CASES, config, delta, latent, layer, make_weights, moe, relative_error, write_model
+
+pytestmark = pytest.mark.gpu
+
+# rms of the logits' error over rms of the logits, per position
+FP32_BOUND = 1e-4
+BF16_BOUND = 5e-2
+LENGTHS = [70, 45, 101, 38, 64, 83, 9, 55, 2, 1]
+
+
+def expected_rows(cfg, weights, requests):
+    return {name: plain.forward(cfg, weights, tokens, dtype=torch.float64).numpy() for name, tokens in requests.items()}
+
+
+def make_runner(folder, dtype, *, page_size, num_pages, max_requests=4, decode_mode="eager", max_model_len=2048):
+    from kairyu_b200.cache import CacheLayout, CacheManager, CacheStorage
+    from kairyu_b200.engine.engine import load_model
+    from kairyu_b200.engine.runner import ModelRunner
+
+    model, _ = load_model(folder, dtype=dtype, device="cuda")
+    layout = CacheLayout.from_slot_specs(model.cache_slot_specs())
+    cache = CacheManager(layout, num_pages=num_pages, page_size=page_size, max_requests=max_requests)
+    storage = CacheStorage(layout, num_pages=num_pages, page_size=page_size, max_requests=max_requests, dtype=model.dtype, device="cuda")
+    return ModelRunner(model, cache, storage, max_model_len=max_model_len, decode_mode=decode_mode, max_graph_batch=max_requests,
+                       check_tables=True, debug_poison=True)
+
+
+def worst(result, expected):
+    return max(relative_error(row, expected[name][position]) for (name, position), row in result.items())
+
+
+def judge(result, expected, dtype, what=""):
+    """float32: every position within the bound.  bfloat16: these weights make the softmax pick single
+    keys and the routers choose among close logits, so that faults show; rounding to bfloat16 then
+    costs a few per cent at a typical position and much more where a close call between two experts
+    turns.  A fault (a window one token off, a lost state) moves the MEDIAN position to 0.16-0.49
+    (test_makilorn_cpu.py), so the median is held to BF16_BOUND and few positions may be far off."""
+    errors = np.array([relative_error(row, expected[name][position]) for (name, position), row in result.items()])
+    if str(dtype).endswith("float32"):
+        print(f"[makilorn] {what} float32: worst {errors.max():.3e} bound {FP32_BOUND:.1e}")
+        assert errors.max() < FP32_BOUND, (what, errors.max(), beyond(result, expected, FP32_BOUND))
+    else:
+        far = float((errors >= 3 * BF16_BOUND).mean())
+        print(f"[makilorn] {what} bfloat16: median {np.median(errors):.3e} worst {errors.max():.3e} far off {far:.3f} bound {BF16_BOUND:.1e}")
+        assert np.median(errors) < BF16_BOUND and far <= 0.05, (what, np.median(errors), far, beyond(result, expected, 3 * BF16_BOUND))
+
+
+def beyond(result, expected, bound):
+    errors = [(name, position, relative_error(row, expected[name][position])) for (name, position), row in result.items()]
+    return [entry for entry in errors if not entry[2] < bound][:12]
+
+
+@pytest.fixture(scope="module", params=list(CASES))
+def case(request, tmp_path_factory):
+    cfg, seed, page_size = CASES[request.param]
+    weights = make_weights(cfg, seed)
+    folder = write_model(cfg, weights, tmp_path_factory.mktemp(request.param))
+    requests = traces.make_requests(cfg["vocab"], LENGTHS, seed=seed + 100)
+    return dict(name=request.param, cfg=cfg, page_size=page_size, weights=weights, folder=folder, requests=requests,
+                expected=expected_rows(cfg, weights, requests))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("decode_mode", ["eager", "cuda_graph"])
+def test_every_cut_matches_plain(case, dtype, decode_mode):
+    """Whole prompts, tails decoded token by token, portions of changing size and mixed batches, one
+    after the other on one engine whose pool holds far less than all requests (pages and state
+    slots change hands; pages that went back are overwritten before the next step)."""
+    requests = case["requests"]
+    cuts = {
+        "whole": traces.trace_whole(requests),
+        "tail": traces.trace_decode_tail(requests, 32),
+        "chunks": traces.trace_chunks(requests),
+        "twos": traces.trace_chunks(requests, sizes=(2,)),
+        "mixed": traces.trace_mixed(requests, seed=5),
+    }
+    pool = max(traces.peak_tokens(steps) for steps in cuts.values()) // case["page_size"] + 1
+    total = sum(len(t) for t in requests.values())
+    assert pool * case["page_size"] < total
+    runner = make_runner(case["folder"], dtype, page_size=case["page_size"], num_pages=pool, decode_mode=decode_mode)
+    results = {}
+    for cut, steps in cuts.items():
+        results[cut] = traces.run_in_process(runner, steps)
+        assert len(results[cut]) == total
+        judge(results[cut], case["expected"], dtype, f"{case['name']} {decode_mode} {cut}")
+    if decode_mode == "cuda_graph":
+        assert runner.counters["graph_replays"] > 0
+    if dtype == "float32":
+        # no 32-bit sum depends on the batch or on where a prompt was cut
+        for cut in ("tail", "chunks", "twos", "mixed"):
+            different = [key for key, row in results["whole"].items() if not np.array_equal(row, results[cut][key])]
+            assert not different, (cut, different[:12])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("kind", ["latent", "latent_wide", "delta", "delta_shared_heads"])
+def test_one_mixer_alone(kind, dtype, tmp_path):
+    """A model of one layer without feed-forward, so that the mixer is all that mixes: a prompt of
+    several windows' length in one step, then decoding over more than a window."""
+    mixers = {
+        "latent": latent(2, 16, 24, 48, 19, 0.5),
+        "latent_wide": latent(3, 32, 32, 128, 70, 0.25),  # rank 128: the two-tile tcgen05 kernel's size
+        "delta": delta(2, 2, 16, 16, 4),
+        "delta_shared_heads": delta(6, 2, 40, 72, 3),    # three heads a query/key head; more columns than a block's 32
+    }
+    cfg = config(40, 53, [layer(mixers[kind], None)])
+    weights = make_weights(cfg, 7)
+    folder = write_model(cfg, weights, tmp_path / kind)
+    tokens = traces.make_requests(53, [230], seed=3)["r0"]
+    expected = {"r0": plain.forward(cfg, weights, tokens, dtype=torch.float64).numpy()}
+    steps = traces.trace_decode_tail({"r0": tokens}, 90)
+    runner = make_runner(folder, dtype, page_size=16, num_pages=20, decode_mode="cuda_graph")
+    result = traces.run_in_process(runner, steps)
+    judge(result, expected, dtype, f"{kind} alone")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("sizes", [(40, 5, 2, 24, 1.25, 33), (64, 8, 8, 16, 0.5, 3), (24, 1, 1, 70, 2.0, 130), (96, 16, 3, 96, 1.5, 700)])
+def test_mixture_of_experts_alone(sizes, dtype):
+    """The part by itself, rows summed here (``combine=True``) and handed on weighted."""
+    from kairyu_b200.engine.workspace import Workspace
+    from kairyu_b200.parts import FEED_FORWARDS, PartSpec, StepContext
+
+    width, experts, top, ff, limit, tokens = sizes
+    cfg = config(width, 11, [layer(latent(1, 8, 8, 16, 4, 1.0), moe(experts, top, ff, limit))])
+    weights = {name: t for name, t in make_weights(cfg, 3).items() if name.startswith("l0.mlp")}
+    part = FEED_FORWARDS.build(PartSpec("moe", prefix="l0.mlp", hidden_size=width, intermediate_size=ff, num_experts=experts, top=top, limit=limit),
+                               dtype=dtype, device="cuda", shared={})
+    part.load({name: t.to(device="cuda", dtype=dtype) for name, t in weights.items()})
+    x = torch.randn(tokens, width, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).float()
+    ctx = StepContext(num_tokens=tokens, num_rows=1, dtype=dtype, token_ids=None, positions=None, row_ids=None, qo_indptr=None, seq_lens=None,
+                      write_from=None, state_slots=None, block_tables={}, host_qo_indptr=(), host_seq_lens=(), workspace=Workspace("cuda"))
+    want = plain.expert_mixture(x.double(), {n: t.double() for n, t in weights.items()}, "l0.mlp", cfg["layers"][0]["mlp"]).numpy()
+    got = part.forward(x.to(device="cuda", dtype=dtype), ctx).float().cpu().numpy()
+    handed = part.forward(x.to(device="cuda", dtype=dtype), ctx, combine=False)
+    summed = (handed.rows.view(tokens, top, width) * handed.weights.unsqueeze(-1)).sum(1).cpu().numpy()
+    bound = 1e-5 if dtype == torch.float32 else 2e-2
+    scale = np.abs(want).max()
+    assert np.abs(got - want).max() < bound * scale
+    assert np.abs(summed - want).max() < bound * scale
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_output_norm_kernel(dtype):
+    from kairyu_b200 import kernels
+
+    tokens, width, k = 37, 200, 3
+    g = torch.Generator().manual_seed(2)
+    residual = torch.randn(tokens, width, generator=g)
+    y = torch.randn(tokens, width, generator=g).to(dtype)
+    weight = (1 + 0.1 * torch.randn(width, generator=g)).to(dtype)
+    want = residual.double() + plain.rms_norm(y.double(), weight.double(), 1e-5)
+    x = residual.cuda()
+    copy = torch.empty(tokens, width, dtype=dtype, device="cuda")
+    kernels.output_norm_add(x, y.cuda(), weight.cuda(), 1e-5, copy)
+    assert (x.cpu().double() - want).abs().max() < 1e-5
+    assert torch.equal(copy.cpu(), x.cpu().to(dtype))
+    rows = torch.randn(tokens * k, width, generator=g)
+    mix = torch.rand(tokens, k, generator=g)
+    summed = (rows.view(tokens, k, width).double() * mix.double().unsqueeze(-1)).sum(1)
+    want = residual.double() + plain.rms_norm(summed, weight.double(), 1e-5)
+    x = residual.cuda()
+    kernels.output_norm_add(x, kernels.WeightedRows(rows.cuda(), mix.cuda()), weight.cuda(), 1e-5, None)
+    assert (x.cpu().double() - want).abs().max() < 1e-5
+
+
+def test_state_does_not_leak_between_requests(tmp_path):
+    """Two state slots, six requests one after the other in pairs: a slot's memory and kept inputs
+    are another request's leftovers unless they are cleared when the slot changes hands."""
+    cfg = config(32, 41, [layer(delta(2, 1, 16, 24, 4), moe(4, 2, 16, 1.0)), layer(latent(2, 8, 8, 16, 11, 0.5), None)])
+    weights = make_weights(cfg, 21)
+    folder = write_model(cfg, weights, tmp_path / "m")
+    requests = traces.make_requests(41, [30, 17, 25, 40, 12, 33], seed=8)
+    expected = expected_rows(cfg, weights, requests)
+    runner = make_runner(folder, "float32", page_size=8, num_pages=12, max_requests=2)
+    result = traces.run_in_process(runner, traces.trace_mixed(requests, seed=2, max_live=2))
+    assert worst(result, expected) < FP32_BOUND, beyond(result, expected, FP32_BOUND)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_through_the_engine(case, dtype):
+    """``LLM.generate`` with a token budget that cuts the prompts into portions and batches them with
+    decoding requests; greedy tokens against the plain model's own greedy continuation."""
+    from kairyu_b200.entrypoints.llm import LLM
+    from kairyu_b200.entrypoints.prompt import TokensPrompt
+    from kairyu_b200.sampling.params import SamplingParams
+
+    cfg, weights = case["cfg"], case["weights"]
+    prompts = [tokens for tokens in list(case["requests"].values())[:6]]
+    new = 12
+    llm = LLM(model=str(case["folder"]), dtype=dtype, num_pages=64, page_size=case["page_size"], max_num_batched_tokens=24,
+              max_num_seqs=4, max_model_len=256)
+    outputs = llm.generate([TokensPrompt(prompt_token_ids=tokens) for tokens in prompts],
+                           SamplingParams(temperature=0.0, max_tokens=new, ignore_eos=True), use_tqdm=False)
+    for tokens, output in zip(prompts, outputs):
+        got = list(output.outputs[0].token_ids)
+        assert len(got) == new
+        # teacher-forced: at every step the engine's choice is (nearly) the plain model's best given the engine's own history
+        logits = plain.forward(cfg, weights, list(tokens) + got, dtype=torch.float64).numpy()
+        close = []
+        for step, token in enumerate(got):
+            row = logits[len(tokens) - 1 + step]
+            close.append((row.max() - row[token]) / row.std())
+        if dtype == "float32":
+            assert max(close) <= 1e-4, close
+        else:  # bfloat16 may turn a close call (and a close call between experts moves a whole row): most steps agree
+            assert np.mean(np.array(close) <= 0.15) >= 0.8, close
+
+
+def test_trace_program(case, tmp_path):
+    """The same through ``bin/trace_run``: four state slots, a pool for the trace's peak."""
+    steps = traces.trace_mixed(case["requests"], seed=9)
+    result = traces.run_program(case["folder"], tmp_path / "out", steps, dtype="float32", max_tokens=traces.peak_tokens(steps), vocab=case["cfg"]["vocab"],
+                                extra=["--page-size", str(case["page_size"])])
+    assert worst(result, case["expected"]) < FP32_BOUND

@@ -40,7 +40,8 @@ def trace_decode_tail(requests: Mapping[str, list[int]], tail: int = 32) -> list
     steps = []
     for name, tokens in requests.items():
         head = max(len(tokens) - tail, 1)
-        steps.append({"step": len(steps), "entries": [{"id": name, "tokens": tokens[:head], "want": list(range(head))}], "end": []})
+        steps.append({"step": len(steps), "entries": [{"id": name, "tokens": tokens[:head], "want": list(range(head))}],
+                      "end": [name] if head == len(tokens) else []})  # a request of one token ends with its first step
         for index in range(head, len(tokens)):
             last = index == len(tokens) - 1
             steps.append(
