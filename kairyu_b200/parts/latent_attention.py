@@ -84,8 +84,10 @@ class LatentAttention(Mixer):
         # one "head" of kv_rank columns a position and no value rows of their own
         return (PagedKVSpec(1, self.kv_rank, self.window, v_head_dim=0),)
 
+    HEADS_PER_CALL = 16  # the tensor-core attention kernels take up to 16 query heads a key/value head
+
     def _tensor_cores(self) -> bool:
-        return self.dtype == torch.bfloat16 and kernels.attention_mma_supported(self.kv_rank, self.num_heads, 1)
+        return self.dtype == torch.bfloat16 and kernels.attention_mma_supported(self.kv_rank, min(self.num_heads, self.HEADS_PER_CALL), 1)
 
     def query_tile_sizes(self) -> tuple[int, ...]:
         if not self._tensor_cores():
@@ -109,7 +111,13 @@ class LatentAttention(Mixer):
         kernels.heads_linear(packed[:, : self.q_size].unflatten(1, (heads, self.head_dim)), self.w_absorb, q_latent.view(tokens, heads, rank))
         mixed = ws.buffer("latent.mixed", tokens, heads * rank, self.dtype)
         rows = CacheView(k=cache.k, v=cache.k, page_size=cache.page_size, group=cache.group, writes=False)
-        run_paged_attention(q_latent, mixed, rows, ctx, num_q_heads=heads, num_kv_heads=1, head_dim=rank, scale=self.scale, window=self.window or 0)
+        # all heads read the same rows; more heads than a kernel takes go in several calls over column ranges
+        per_call = self.HEADS_PER_CALL if self._tensor_cores() else heads
+        for first in range(0, heads, per_call):
+            count = min(per_call, heads - first)
+            columns = slice(first * rank, (first + count) * rank)
+            run_paged_attention(q_latent[:, columns], mixed[:, columns], rows, ctx, num_q_heads=count, num_kv_heads=1, head_dim=rank,
+                                scale=self.scale, window=self.window or 0)
         values = ws.buffer("latent.values", tokens, heads * self.value_dim, self.dtype)
         kernels.heads_linear(mixed.view(tokens, heads, rank), self.w_up_v, values.view(tokens, heads, self.value_dim))
         out = ws.buffer("latent.out", tokens, self.hidden_size, self.dtype)

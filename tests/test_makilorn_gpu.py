@@ -55,7 +55,7 @@ def judge(result, expected, dtype, what=""):
     else:
         far = float((errors >= 3 * BF16_BOUND).mean())
         print(f"[makilorn] {what} bfloat16: median {np.median(errors):.3e} worst {errors.max():.3e} far off {far:.3f} bound {BF16_BOUND:.1e}")
-        assert np.median(errors) < BF16_BOUND and far <= 0.05, (what, np.median(errors), far, beyond(result, expected, 3 * BF16_BOUND))
+        assert np.median(errors) < BF16_BOUND and far <= 0.10, (what, np.median(errors), far, beyond(result, expected, 3 * BF16_BOUND))
 
 
 def beyond(result, expected, bound):
