@@ -4,8 +4,11 @@
 //   moe_route     per token: the K largest of (router logits + bias) choose the experts (ties go to
 //                 the lower index); their weights are the softmax over the K chosen logits.  32-bit.
 //   moe_plan      one block: pairs p = t * K + k are counted per expert, the experts' runs are laid
-//                 side by side (`sorted` lists the pairs run by run), and the runs are cut into
-//                 tiles of MOE_TM pairs: tile -> (expert, first place in `sorted`, pairs).
+//                 side by side (`sorted` lists the pairs run by run, `token_of` their tokens,
+//                 `place_of[p]` is where pair p stands, `ends[e]` where expert e's run ends), and
+//                 the runs are cut into tiles of MOE_TM pairs: tile -> (expert, first place, pairs).
+//   moe_activation  y = a * sigmoid(alpha a) * (b + 1) with a = min(gate, limit), b = clamp(up, +-limit)
+//                 over rows [gate columns | up columns]: for the path whose products are a library's.
 //   moe_grouped   one block per (tile, 64 output columns): a [pairs, K] x [K, 64] product with the
 //                 tile's expert's weight.  Gated form: A rows are the tokens' activations (gathered
 //                 through the pair list), the weight holds the expert's gate rows and then its up
@@ -16,7 +19,7 @@
 //                 together and whoever adds them (weighted by the router) does so in the order of k.
 //                 bfloat16 runs on mma.sync m16n8k16 with 32-bit accumulators, float32 on FMAs; the
 //                 sum over K runs in ascending order in both, whatever else the tile holds.
-//   moe_combine   out[t] = sum_k weight[t, k] * rows[t * K + k]   (for callers that want plain rows)
+//   moe_combine   out[t] = sum_k weight[t, k] * rows[at(t * K + k)]   (for callers that want plain rows)
 #include "common.cuh"
 
 #define MOE_TM 64
@@ -74,8 +77,15 @@ moe_route_kernel(const float* __restrict__ logits, const TB* __restrict__ bias, 
     }
 }
 
+__device__ __forceinline__ float expert_activation(float gate, float up, float limit, float alpha) {
+    const float a = fminf(gate, limit);
+    const float b = fminf(fmaxf(up, -limit), limit);
+    return a * (1.0f / (1.0f + expf(-alpha * a))) * (b + 1.0f);
+}
+
 __global__ void __launch_bounds__(1024)
-moe_plan_kernel(const int* __restrict__ ids, int pairs, int E, int* __restrict__ sorted, int* __restrict__ tile_expert,
+moe_plan_kernel(const int* __restrict__ ids, int pairs, int E, int top, int* __restrict__ sorted, int* __restrict__ token_of,
+                int* __restrict__ place_of, int* __restrict__ ends, int* __restrict__ tile_expert,
                 int* __restrict__ tile_first, int* __restrict__ tile_pairs, int* __restrict__ num_tiles) {
     __shared__ int counts[MOE_MAX_EXPERTS];
     __shared__ int cursor[MOE_MAX_EXPERTS];
@@ -95,13 +105,30 @@ moe_plan_kernel(const int* __restrict__ ids, int pairs, int E, int* __restrict__
                 ++tiles;
             }
             at += counts[e];
+            ends[e] = at;
         }
         *num_tiles = tiles;
     }
     __syncthreads();
     // The order of the pairs inside an expert's run is whatever the additions below give; a pair's
     // result does not depend on its place in a tile.
-    for (int p = threadIdx.x; p < pairs; p += blockDim.x) sorted[atomicAdd(&cursor[ids[p]], 1)] = p;
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int place = atomicAdd(&cursor[ids[p]], 1);
+        sorted[place] = p;
+        token_of[place] = p / top;
+        place_of[p] = place;
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_activation_kernel(const T* __restrict__ gate_up, T* __restrict__ y, int F, float limit, float alpha, size_t total) {
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t row = i / F, col = i % F;
+    const float gate = to_float(gate_up[row * 2 * F + col]), up = to_float(gate_up[row * 2 * F + F + col]);
+    y[i] = from_float<T>(expert_activation(gate, up, limit, alpha));
 }
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
@@ -111,11 +138,6 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
-__device__ __forceinline__ float expert_activation(float gate, float up, float limit, float alpha) {
-    const float a = fminf(gate, limit);
-    const float b = fminf(fmaxf(up, -limit), limit);
-    return a * (1.0f / (1.0f + expf(-alpha * a))) * (b + 1.0f);
-}
 
 // 8 bfloat16 (or 4 float) of a row into shared memory, zeros beyond the row's end or for a row that is not there
 __device__ __forceinline__ void stage_chunk(__nv_bfloat16* dst, const __nv_bfloat16* row, int k, int Kd, bool vec) {
@@ -297,14 +319,18 @@ moe_grouped_kernel(const T* __restrict__ A, int lda, const int* __restrict__ sor
     }
 }
 
-template <typename TO>
+template <typename TR, typename TO>
 __global__ void __launch_bounds__(256)
-moe_combine_kernel(const float* __restrict__ rows, const float* __restrict__ weights, int K, int H, TO* __restrict__ out) {
+moe_combine_kernel(const TR* __restrict__ rows, const float* __restrict__ weights, const int* __restrict__ at, int K, int H,
+                   TO* __restrict__ out) {
     pdl_wait();
     const int t = blockIdx.x;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         float v = 0.0f;
-        for (int k = 0; k < K; ++k) v += weights[(size_t)t * K + k] * rows[((size_t)t * K + k) * H + i];
+        for (int k = 0; k < K; ++k) {
+            const size_t p = (size_t)t * K + k;
+            v += weights[p] * to_float(rows[(at ? (size_t)at[p] : p) * H + i]);
+        }
         out[(size_t)t * H + i] = from_float<TO>(v);
     }
 }
@@ -323,12 +349,25 @@ KB_EXPORT int kb_moe_route(const float* logits, const void* bias, int bias_is_bf
 
 KB_EXPORT int kb_moe_max_tiles(int pairs, int E) { return (pairs + MOE_TM - 1) / MOE_TM + E; }
 
-KB_EXPORT int kb_moe_plan(const int* ids, int pairs, int E, int* sorted, int* tile_expert, int* tile_first, int* tile_pairs,
-                          int* num_tiles, cudaStream_t stream) {
+KB_EXPORT int kb_moe_plan(const int* ids, int pairs, int E, int top, int* sorted, int* token_of, int* place_of, int* ends,
+                          int* tile_expert, int* tile_first, int* tile_pairs, int* num_tiles, cudaStream_t stream) {
     if (pairs == 0) return 0;
-    if (!ids || !sorted || !tile_expert || !tile_first || !tile_pairs || !num_tiles) return KB_ERR_NULL;
-    if (E < 1 || E > MOE_MAX_EXPERTS) return KB_ERR_UNSUPPORTED_SIZE;
-    kb_launch(moe_plan_kernel, dim3(1), dim3(1024), 0, stream, ids, pairs, E, sorted, tile_expert, tile_first, tile_pairs, num_tiles);
+    if (!ids || !sorted || !token_of || !place_of || !ends || !tile_expert || !tile_first || !tile_pairs || !num_tiles) return KB_ERR_NULL;
+    if (E < 1 || E > MOE_MAX_EXPERTS || top < 1) return KB_ERR_UNSUPPORTED_SIZE;
+    kb_launch(moe_plan_kernel, dim3(1), dim3(1024), 0, stream, ids, pairs, E, top, sorted, token_of, place_of, ends, tile_expert, tile_first,
+              tile_pairs, num_tiles);
+    return kb_launch_result();
+}
+
+KB_EXPORT int kb_moe_activation(const void* gate_up, void* y, int is_bf16, int rows, int F, float limit, float alpha, cudaStream_t stream) {
+    if (rows == 0) return 0;
+    if (!gate_up || !y) return KB_ERR_NULL;
+    const size_t total = (size_t)rows * F;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (is_bf16)
+        kb_launch(moe_activation_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)y, F, limit, alpha, total);
+    else
+        kb_launch(moe_activation_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)gate_up, (float*)y, F, limit, alpha, total);
     return kb_launch_result();
 }
 
@@ -353,13 +392,16 @@ KB_EXPORT int kb_moe_grouped(const void* A, int lda, const int* sorted, int top,
     return kb_launch_result();
 }
 
-KB_EXPORT int kb_moe_combine(const float* rows, const float* weights, int K, int H, void* out, int out_is_bf16, int T,
-                             cudaStream_t stream) {
+KB_EXPORT int kb_moe_combine(const void* rows, int rows_is_bf16, const float* weights, const int* at, int K, int H, void* out,
+                             int out_is_bf16, int T, cudaStream_t stream) {
     if (T == 0) return 0;
     if (!rows || !weights || !out) return KB_ERR_NULL;
-    if (out_is_bf16)
-        kb_launch(moe_combine_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, rows, weights, K, H, (__nv_bfloat16*)out);
-    else
-        kb_launch(moe_combine_kernel<float>, dim3(T), dim3(256), 0, stream, rows, weights, K, H, (float*)out);
+#define LAUNCH(TR, TO) kb_launch(moe_combine_kernel<TR, TO>, dim3(T), dim3(256), 0, stream, (const TR*)rows, weights, at, K, H, (TO*)out)
+    if (rows_is_bf16) {
+        if (out_is_bf16) LAUNCH(__nv_bfloat16, __nv_bfloat16); else LAUNCH(__nv_bfloat16, float);
+    } else {
+        if (out_is_bf16) LAUNCH(float, __nv_bfloat16); else LAUNCH(float, float);
+    }
+#undef LAUNCH
     return kb_launch_result();
 }

@@ -1,6 +1,7 @@
 // A norm on a sub-layer's OUTPUT, with the residual sum behind it:
 //
-//     y[t]  = sum_k mix[t, k] * parts[t * K + k]          (K = 1 and no mix: y = parts)
+//     y[t]  = sum_k mix[t, k] * parts[at(t * K + k)]      (K = 1 and no mix: y = parts; at: an optional
+//                                                          index of where each of the K rows lies)
 //     x[t] += y[t] * rsqrt(mean(y[t]^2) + eps) * w         (x: the fp32 residual stream)
 //     copy[t] = x[t] in the activation dtype               (what the next sub-layer's products read)
 //
@@ -14,7 +15,7 @@
 template <typename TY, typename TW, typename TC>
 __global__ void __launch_bounds__(256)
 output_norm_add_kernel(float* __restrict__ x, const TY* __restrict__ parts, const float* __restrict__ mix,
-                       int K, const TW* __restrict__ w, TC* __restrict__ copy, int H, float eps) {
+                       const int* __restrict__ at, int K, const TW* __restrict__ w, TC* __restrict__ copy, int H, float eps) {
     extern __shared__ float row[];
     __shared__ float scratch[32];
     pdl_wait();
@@ -24,7 +25,10 @@ output_norm_add_kernel(float* __restrict__ x, const TY* __restrict__ parts, cons
         float v;
         if (mix) {
             v = 0.0f;
-            for (int k = 0; k < K; ++k) v += mix[(size_t)t * K + k] * to_float(parts[((size_t)t * K + k) * H + i]);
+            for (int k = 0; k < K; ++k) {
+                const size_t p = (size_t)t * K + k;
+                v += mix[p] * to_float(parts[(at ? (size_t)at[p] : p) * H + i]);
+            }
         } else {
             v = to_float(parts[(size_t)t * H + i]);
         }
@@ -42,29 +46,29 @@ output_norm_add_kernel(float* __restrict__ x, const TY* __restrict__ parts, cons
 }
 
 template <typename TY, typename TW>
-static int launch_output_norm(float* x, const void* parts, const float* mix, int K, const void* w, void* copy,
+static int launch_output_norm(float* x, const void* parts, const float* mix, const int* at, int K, const void* w, void* copy,
                               int copy_is_bf16, int T, int H, float eps, cudaStream_t stream) {
     const size_t smem = (size_t)H * sizeof(float);
     if (copy_is_bf16)
-        kb_launch(output_norm_add_kernel<TY, TW, __nv_bfloat16>, dim3(T), dim3(256), smem, stream, x, (const TY*)parts, mix, K,
+        kb_launch(output_norm_add_kernel<TY, TW, __nv_bfloat16>, dim3(T), dim3(256), smem, stream, x, (const TY*)parts, mix, at, K,
                   (const TW*)w, (__nv_bfloat16*)copy, H, eps);
     else
-        kb_launch(output_norm_add_kernel<TY, TW, float>, dim3(T), dim3(256), smem, stream, x, (const TY*)parts, mix, K,
+        kb_launch(output_norm_add_kernel<TY, TW, float>, dim3(T), dim3(256), smem, stream, x, (const TY*)parts, mix, at, K,
                   (const TW*)w, (float*)copy, H, eps);
     return kb_launch_result();
 }
 
-KB_EXPORT int kb_output_norm_add(float* x, const void* parts, int parts_is_bf16, const float* mix, int K, const void* w,
+KB_EXPORT int kb_output_norm_add(float* x, const void* parts, int parts_is_bf16, const float* mix, const int* at, int K, const void* w,
                                  int w_is_bf16, void* copy, int copy_is_bf16, int T, int H, float eps, cudaStream_t stream) {
     if (T == 0) return 0;
     if (!x || !parts || !w) return KB_ERR_NULL;
     if (H < 1 || H > 12000 || K < 1) return KB_ERR_UNSUPPORTED_SIZE;  // the row lives in 48 KB of shared memory
     if (parts_is_bf16) {
-        if (w_is_bf16) return launch_output_norm<__nv_bfloat16, __nv_bfloat16>(x, parts, mix, K, w, copy, copy_is_bf16, T, H, eps, stream);
-        return launch_output_norm<__nv_bfloat16, float>(x, parts, mix, K, w, copy, copy_is_bf16, T, H, eps, stream);
+        if (w_is_bf16) return launch_output_norm<__nv_bfloat16, __nv_bfloat16>(x, parts, mix, at, K, w, copy, copy_is_bf16, T, H, eps, stream);
+        return launch_output_norm<__nv_bfloat16, float>(x, parts, mix, at, K, w, copy, copy_is_bf16, T, H, eps, stream);
     }
-    if (w_is_bf16) return launch_output_norm<float, __nv_bfloat16>(x, parts, mix, K, w, copy, copy_is_bf16, T, H, eps, stream);
-    return launch_output_norm<float, float>(x, parts, mix, K, w, copy, copy_is_bf16, T, H, eps, stream);
+    if (w_is_bf16) return launch_output_norm<float, __nv_bfloat16>(x, parts, mix, at, K, w, copy, copy_is_bf16, T, H, eps, stream);
+    return launch_output_norm<float, float>(x, parts, mix, at, K, w, copy, copy_is_bf16, T, H, eps, stream);
 }
 
 // copy[t] = x[t] in bfloat16: the first sub-layer of a model reads the embedding's rows.

@@ -1136,33 +1136,38 @@ class ResidualCopy:
 @dataclass
 class WeightedRows:
     """A sub-layer's output as K rows a token and their weights (a mixture of experts before the
-    sum): ``rows`` [tokens * K, width] fp32, ``weights`` [tokens, K] fp32."""
+    sum): ``rows`` [tokens * K, width], ``weights`` [tokens, K] fp32; row k of token t is
+    ``rows[t * K + k]``, or ``rows[at[t * K + k]]`` where ``at`` (int32) is given."""
 
     rows: torch.Tensor
     weights: torch.Tensor
+    at: Optional[torch.Tensor] = None
 
 
 def output_norm_add(residual: torch.Tensor, y, weight: torch.Tensor, eps: float, copy: Optional[torch.Tensor]) -> None:
     """``residual += rmsnorm(y) * weight`` and ``copy = residual`` in the activation dtype (when given).
     ``y``: rows of the residual's shape, or a :class:`WeightedRows` whose K rows a token are summed
     first, weighted, in the order of k."""
-    mix = None
+    mix = at = None
     K = 1
     rows = y
     if isinstance(y, WeightedRows):
-        rows, mix = y.rows, y.weights
+        rows, mix, at = y.rows, y.weights, y.at
         K = mix.shape[1]
+        _need_i32("output_norm_add", at)
+        if at is not None and at.numel() != mix.numel():
+            raise KernelError("output_norm_add: the index of weighted rows must have one entry a row")
         if mix.dtype != torch.float32 or not mix.is_contiguous() or mix.shape[0] != residual.shape[0]:
             raise KernelError("output_norm_add: the weights of weighted rows must be contiguous fp32 [tokens, K]")
-    _need_cuda("output_norm_add", residual, rows, weight, copy, mix)
+    _need_cuda("output_norm_add", residual, rows, weight, copy, mix, at)
     T, H = residual.shape
     if residual.dtype != torch.float32 or not residual.is_contiguous() or not rows.is_contiguous() or rows.shape != (T * K, H):
         raise KernelError("output_norm_add: the residual must be contiguous fp32 and the rows of its width")
     if weight.numel() != H or (copy is not None and (copy.shape != (T, H) or not copy.is_contiguous())):
         raise KernelError("output_norm_add: shape mismatch")
-    fn = _fn("sublayer_norm", "kb_output_norm_add", [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
+    fn = _fn("sublayer_norm", "kb_output_norm_add", [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
     _check(
-        fn(residual.data_ptr(), rows.data_ptr(), _is_bf16(rows, "output_norm_add"), _ptr(mix), K, weight.data_ptr(),
+        fn(residual.data_ptr(), rows.data_ptr(), _is_bf16(rows, "output_norm_add"), _ptr(mix), _ptr(at), K, weight.data_ptr(),
            _is_bf16(weight, "output_norm_add"), _ptr(copy), _is_bf16(copy, "output_norm_add") if copy is not None else 0, T, H,
            float(eps), _stream()),
         "output_norm_add",
@@ -1359,26 +1364,58 @@ def moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], top: int, ids:
 
 
 def moe_plan(ids: torch.Tensor, experts: int, plan: torch.Tensor) -> dict:
-    """Sort a step's (token, expert) pairs by expert and cut the runs into tiles.  ``plan``: int32
-    scratch of at least ``pairs + 3 * moe_max_tiles + 1`` entries; returns views into it."""
+    """Sort a step's (token, expert) pairs by expert and cut the runs into tiles.  ``ids`` [tokens, top];
+    ``plan``: int32 scratch of at least ``moe_plan_size(pairs, experts)`` entries; returns views into it:
+    ``sorted`` (the pairs run by run), ``token_of`` (their tokens), ``place_of`` (where each pair stands),
+    ``ends`` (where each expert's run ends) and the tile lists."""
     _need_cuda("moe_plan", ids, plan)
     _need_i32("moe_plan", ids, plan)
+    top = ids.shape[1]
     pairs = ids.numel()
     tiles = moe_max_tiles(pairs, experts)
-    if plan.numel() < pairs + 3 * tiles + 1:
+    if plan.numel() < moe_plan_size(pairs, experts):
         raise KernelError("moe_plan: the scratch is too small")
-    views = {
-        "sorted": plan[:pairs],
-        "tile_expert": plan[pairs : pairs + tiles],
-        "tile_first": plan[pairs + tiles : pairs + 2 * tiles],
-        "tile_pairs": plan[pairs + 2 * tiles : pairs + 3 * tiles],
-        "num_tiles": plan[pairs + 3 * tiles : pairs + 3 * tiles + 1],
-        "max_tiles": tiles,
-    }
-    fn = _fn("moe", "kb_moe_plan", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
-    _check(fn(ids.data_ptr(), pairs, int(experts), views["sorted"].data_ptr(), views["tile_expert"].data_ptr(), views["tile_first"].data_ptr(),
-              views["tile_pairs"].data_ptr(), views["num_tiles"].data_ptr(), _stream()), "moe_plan")
+    views: dict = {"max_tiles": tiles}
+    at = 0
+    for name, count in (("sorted", pairs), ("token_of", pairs), ("place_of", pairs), ("ends", experts), ("tile_expert", tiles),
+                        ("tile_first", tiles), ("tile_pairs", tiles), ("num_tiles", 1)):
+        views[name] = plan[at : at + count]
+        at += count
+    fn = _fn("moe", "kb_moe_plan", [c_void_p, c_int, c_int, c_int] + [c_void_p] * 9)
+    _check(fn(ids.data_ptr(), pairs, int(experts), int(top), views["sorted"].data_ptr(), views["token_of"].data_ptr(), views["place_of"].data_ptr(),
+              views["ends"].data_ptr(), views["tile_expert"].data_ptr(), views["tile_first"].data_ptr(), views["tile_pairs"].data_ptr(),
+              views["num_tiles"].data_ptr(), _stream()), "moe_plan")
     return views
+
+
+def moe_plan_size(pairs: int, experts: int) -> int:
+    return 3 * pairs + experts + 3 * moe_max_tiles(pairs, experts) + 1
+
+
+def moe_library_products_ok(hidden: int, intermediate: int, dtype: torch.dtype) -> bool:
+    """Whether the experts' products can go to the library's grouped product (bfloat16, fp32
+    accumulation, group sizes read on the device): it wants every row 16-byte aligned."""
+    return dtype == torch.bfloat16 and hidden % 8 == 0 and intermediate % 8 == 0 and hasattr(torch, "_grouped_mm")
+
+
+def moe_library_product(a: torch.Tensor, weight: torch.Tensor, ends: torch.Tensor) -> torch.Tensor:
+    """Rows of ``a`` [pairs, K], sorted by expert, times their experts' weights ``weight`` [experts, N, K]:
+    [pairs, N] bfloat16.  ``ends`` (int32, on the device) gives where each expert's rows end."""
+    _need_cuda("moe_library_product", a, weight, ends)
+    if a.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or not a.is_contiguous() or not weight.is_contiguous():
+        raise KernelError("moe_library_product: contiguous bfloat16 operands only")
+    return torch._grouped_mm(a, weight.transpose(1, 2), offs=ends)
+
+
+def moe_activation(gate_up: torch.Tensor, out: torch.Tensor, *, limit: float, alpha: float = 1.702) -> None:
+    """out = a * sigmoid(alpha a) * (b + 1), a = min(gate, limit), b = clamp(up, -limit, limit); ``gate_up`` rows hold
+    the gate columns and then the up columns."""
+    _need_cuda("moe_activation", gate_up, out)
+    rows, wide = gate_up.shape
+    if wide % 2 or out.shape != (rows, wide // 2) or out.dtype != gate_up.dtype or not (gate_up.is_contiguous() and out.is_contiguous()):
+        raise KernelError("moe_activation: shape or dtype mismatch")
+    fn = _fn("moe", "kb_moe_activation", [c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p])
+    _check(fn(gate_up.data_ptr(), out.data_ptr(), _is_bf16(out, "moe_activation"), rows, wide // 2, float(limit), float(alpha), _stream()), "moe_activation")
 
 
 def moe_grouped(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, plan: dict, *, top: int, gated: bool, limit: float = 0.0,
@@ -1402,12 +1439,13 @@ def moe_grouped(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, plan: 
               plan["max_tiles"], float(limit), float(alpha), out.data_ptr(), _stream()), "moe_grouped")
 
 
-def moe_combine(rows: torch.Tensor, weights: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t] = sum_k weights[t, k] * rows[t * K + k] (fp32 sum, in the order of k)."""
-    _need_cuda("moe_combine", rows, weights, out)
+def moe_combine(rows: torch.Tensor, weights: torch.Tensor, out: torch.Tensor, at: Optional[torch.Tensor] = None) -> None:
+    """out[t] = sum_k weights[t, k] * rows[t * K + k] (or rows[at[t * K + k]]): fp32 sum, in the order of k."""
+    _need_cuda("moe_combine", rows, weights, out, at)
+    _need_i32("moe_combine", at)
     T, K = weights.shape
     H = rows.shape[1]
-    if rows.dtype != torch.float32 or weights.dtype != torch.float32 or rows.shape[0] != T * K or out.shape != (T, H) or not (rows.is_contiguous() and weights.is_contiguous() and out.is_contiguous()):
+    if weights.dtype != torch.float32 or rows.shape[0] != T * K or out.shape != (T, H) or not (rows.is_contiguous() and weights.is_contiguous() and out.is_contiguous()):
         raise KernelError("moe_combine: shape or dtype mismatch")
-    fn = _fn("moe", "kb_moe_combine", [c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p])
-    _check(fn(rows.data_ptr(), weights.data_ptr(), K, H, out.data_ptr(), _is_bf16(out, "moe_combine"), T, _stream()), "moe_combine")
+    fn = _fn("moe", "kb_moe_combine", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p])
+    _check(fn(rows.data_ptr(), _is_bf16(rows, "moe_combine"), weights.data_ptr(), _ptr(at), K, H, out.data_ptr(), _is_bf16(out, "moe_combine"), T, _stream()), "moe_combine")

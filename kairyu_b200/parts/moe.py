@@ -6,12 +6,14 @@ the weights are the softmax over the chosen logits only.  An expert is
 ``W_down(a * sigmoid(alpha a) * (b + 1))`` with ``a = min(W_gate x, limit)`` and
 ``b = clamp(W_up x, -limit, limit)``.
 
-A step's (token, expert) pairs are sorted by expert on the device and cut into tiles; one grouped
-product runs gate and up with the activation in its epilogue, a second runs down
-(``csrc/moe.cu``).  Nothing comes back to the host, so the work can sit in a captured graph.  The
-down product leaves one fp32 row per pair; ``forward(..., combine=False)`` hands those and the
-router's weights on (``kernels.WeightedRows``) for a kernel that adds them on its way, otherwise
-they are added here.
+A step's (token, expert) pairs are sorted by expert on the device (``csrc/moe.cu``).  In bfloat16
+with rows of whole 16 bytes the two products of the experts go to the library's grouped product,
+which reads the group sizes on the device, with a gather before, the experts' activation between
+and the rows left in sorted order; float32 and other sizes run this package's own grouped kernels
+(gate and up with the activation in the epilogue, then down).  Nothing comes back to the host, so
+the work can sit in a captured graph.  Either way there is one row per pair at the end;
+``forward(..., combine=False)`` hands those, the router's weights and where each row lies on
+(``kernels.WeightedRows``) for a kernel that adds them on its way, otherwise they are added here.
 """
 
 from __future__ import annotations
@@ -99,14 +101,23 @@ class MixtureOfExperts(FeedForward):
         weights = ws.buffer("moe.weights", tokens, top, torch.float32)
         kernels.moe_route(logits, self.b_router, top, ids, weights)
         pairs = tokens * top
-        scratch = ws.flat("moe.plan", pairs + 3 * kernels.moe_max_tiles(pairs, experts) + 1, torch.int32)
-        plan = kernels.moe_plan(ids.view(-1), experts, scratch)
-        hidden = ws.buffer("moe.hidden", pairs, self.intermediate_size, self.dtype)
-        kernels.moe_grouped(x, self.w_gate_up, hidden, plan, top=top, gated=True, limit=self.limit, alpha=self.alpha)
-        rows = ws.buffer("moe.rows", pairs, self.hidden_size, torch.float32)
-        kernels.moe_grouped(hidden, self.w_down, rows, plan, top=top, gated=False)
+        plan = kernels.moe_plan(ids, experts, ws.flat("moe.plan", kernels.moe_plan_size(pairs, experts), torch.int32))
+        if kernels.moe_library_products_ok(self.hidden_size, self.intermediate_size, self.dtype):
+            # bfloat16, aligned sizes: the tokens' rows are laid out run by run and the library's grouped
+            # product (group sizes read on the device) runs both products; the rows stay in that order
+            gathered = ws.buffer("moe.gathered", pairs, self.hidden_size, self.dtype)
+            kernels.gather_rows(x, plan["token_of"], gathered)
+            gate_up = kernels.moe_library_product(gathered, self.w_gate_up, plan["ends"])
+            hidden = ws.buffer("moe.hidden", pairs, self.intermediate_size, self.dtype)
+            kernels.moe_activation(gate_up, hidden, limit=self.limit, alpha=self.alpha)
+            rows, at = kernels.moe_library_product(hidden, self.w_down, plan["ends"]), plan["place_of"]
+        else:
+            hidden = ws.buffer("moe.hidden", pairs, self.intermediate_size, self.dtype)
+            kernels.moe_grouped(x, self.w_gate_up, hidden, plan, top=top, gated=True, limit=self.limit, alpha=self.alpha)
+            rows, at = ws.buffer("moe.rows", pairs, self.hidden_size, torch.float32), None
+            kernels.moe_grouped(hidden, self.w_down, rows, plan, top=top, gated=False)
         if not combine:
-            return kernels.WeightedRows(rows, weights)
+            return kernels.WeightedRows(rows, weights, at)
         out = ws.buffer("moe.out", tokens, self.hidden_size, self.dtype)
-        kernels.moe_combine(rows, weights, out)
+        kernels.moe_combine(rows, weights, out, at)
         return out

@@ -128,9 +128,11 @@ def test_one_mixer_alone(kind, dtype, tmp_path):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("sizes", [(40, 5, 2, 24, 1.25, 33), (64, 8, 8, 16, 0.5, 3), (24, 1, 1, 70, 2.0, 130), (96, 16, 3, 96, 1.5, 700)])
+@pytest.mark.parametrize("sizes", [(40, 5, 2, 24, 1.25, 33), (64, 8, 8, 16, 0.5, 3), (24, 1, 1, 70, 2.0, 130), (96, 16, 3, 96, 1.5, 700), (40, 6, 2, 20, 1.0, 300)])
 def test_mixture_of_experts_alone(sizes, dtype):
-    """The part by itself, rows summed here (``combine=True``) and handed on weighted."""
+    """The part by itself, rows summed here (``combine=True``) and handed on weighted.  Sizes whose rows
+    are whole 16 bytes take the library's grouped product in bfloat16, the others (70 and 20 rows an
+    expert) this package's tensor-core kernel; float32 always takes the FMA kernel."""
     from kairyu_b200.engine.workspace import Workspace
     from kairyu_b200.parts import FEED_FORWARDS, PartSpec, StepContext
 
@@ -146,7 +148,8 @@ def test_mixture_of_experts_alone(sizes, dtype):
     want = plain.expert_mixture(x.double(), {n: t.double() for n, t in weights.items()}, "l0.mlp", cfg["layers"][0]["mlp"]).numpy()
     got = part.forward(x.to(device="cuda", dtype=dtype), ctx).float().cpu().numpy()
     handed = part.forward(x.to(device="cuda", dtype=dtype), ctx, combine=False)
-    summed = (handed.rows.view(tokens, top, width) * handed.weights.unsqueeze(-1)).sum(1).cpu().numpy()
+    rows = handed.rows.float() if handed.at is None else handed.rows.float()[handed.at.long()]  # where row k of token t lies
+    summed = (rows.view(tokens, top, width) * handed.weights.unsqueeze(-1)).sum(1).cpu().numpy()
     bound = 1e-5 if dtype == torch.float32 else 2e-2
     scale = np.abs(want).max()
     assert np.abs(got - want).max() < bound * scale
