@@ -13,10 +13,12 @@
 //                     that lie before the step's first token), silu, unit norms, beta and g; all
 //                     results 32-bit
 //   delta_conv_state  per request: the last (taps - 1) inputs of the step become the kept inputs
-//   delta_recurrence  per (request, head, 16 columns of S): walks the request's tokens in order.
-//                     Columns of S are independent of one another, so the grid spreads them; eight
-//                     lanes share a column (each holds an eighth of its D entries in registers)
-//                     and the two dot products of a token meet in three shuffles.  With a = S^T k
+//   delta_recurrence  per (request, head, 8 columns of S): walks the request's tokens in order.
+//                     Columns of S are independent of one another, so the grid spreads them: a warp
+//                     owns a column (a lane holds D/32 of its entries in registers) and the two dot
+//                     products of a token meet in a butterfly.  A token is a chain of dependent
+//                     steps whatever the layout, so what counts is how many warps an SM has to
+//                     switch between: a column a warp gives a prompt heads x V of them.  With a = S^T k
 //                     and b = S^T q of the OLD S:  u = beta (v - g a),  o = g b + (k.q) u,
 //                     S = g S + k u^T, which is the recurrence above with one pass over S for the
 //                     dots and one for the update
@@ -28,7 +30,7 @@
 
 #define DELTA_MAX_TAPS 16
 #define DELTA_CHUNK 16
-#define DELTA_LANES 8
+#define DELTA_COLS 8  // columns of S a block owns, one warp each
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
 
@@ -131,46 +133,42 @@ delta_conv_state_kernel(const TA* __restrict__ proj, int stride, float* __restri
 }
 
 template <int DPT>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(32 * DELTA_COLS)
 delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ vv,
                         const float* __restrict__ beta, const float* __restrict__ decay, float* __restrict__ states,
                         const int* __restrict__ qo_indptr, const int* __restrict__ state_slots, int KH, int D, int H, int V,
                         float* __restrict__ out) {
-    constexpr int LANES = DELTA_LANES;          // lanes that share a column of S
-    constexpr int COLS = 128 / LANES;           // columns a block owns
-    constexpr int LD = LANES * (DPT + 4);       // a lane's entries lie 4 floats apart from the next lane's: no bank conflicts
+    constexpr int LD = 32 * DPT;  // entries of a key or query row as staged (zeros beyond D)
     __shared__ __align__(16) float ks[DELTA_CHUNK][LD];
     __shared__ __align__(16) float qs[DELTA_CHUNK][LD];
-    __shared__ float vs[DELTA_CHUNK][COLS];
+    __shared__ float vs[DELTA_CHUNK][DELTA_COLS];
     __shared__ float bs[DELTA_CHUNK], gs[DELTA_CHUNK], kqs[DELTA_CHUNK];
     const int row = blockIdx.x, h = blockIdx.y;
-    const int col0 = blockIdx.z * COLS;
-    const int local = threadIdx.x / LANES;
-    const int col = col0 + local;
-    const int part = threadIdx.x % LANES;
+    const int col0 = blockIdx.z * DELTA_COLS;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int col = col0 + warp;  // a warp owns a column of S; lane l holds its entries l, l + 32, ...
     const int kh = h / (H / KH);
     const int t0 = qo_indptr[row], t1 = qo_indptr[row + 1];
-    float* Sg = states + ((size_t)state_slots[row] * H + h) * D * V;
+    // the state is kept column by column ([heads, V, D]): a warp's column is one run of memory
+    float* Sg = states + (((size_t)state_slots[row] * H + h) * V + (col < V ? col : 0)) * D;
     pdl_wait();
     float S[DPT];
 #pragma unroll
     for (int m = 0; m < DPT; ++m) {
-        const int i = part * DPT + m;
-        S[m] = (i < D && col < V) ? Sg[(size_t)i * V + col] : 0.0f;
+        const int i = m * 32 + lane;
+        S[m] = (i < D && col < V) ? Sg[i] : 0.0f;
     }
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int c0 = t0; c0 < t1; c0 += DELTA_CHUNK) {
         const int nt = min(DELTA_CHUNK, t1 - c0);
         __syncthreads();
-        for (int idx = threadIdx.x; idx < nt * LANES * DPT; idx += blockDim.x) {
-            const int tt = idx / (LANES * DPT), i = idx % (LANES * DPT);
-            const int at = (i / DPT) * (DPT + 4) + (i % DPT);
+        for (int idx = threadIdx.x; idx < nt * LD; idx += blockDim.x) {
+            const int tt = idx / LD, i = idx % LD;
             const size_t src = ((size_t)(c0 + tt) * KH + kh) * D + i;
-            ks[tt][at] = i < D ? kn[src] : 0.0f;
-            qs[tt][at] = i < D ? qn[src] : 0.0f;
+            ks[tt][i] = i < D ? kn[src] : 0.0f;
+            qs[tt][i] = i < D ? qn[src] : 0.0f;
         }
-        for (int idx = threadIdx.x; idx < nt * COLS; idx += blockDim.x) {
-            const int tt = idx / COLS, j = idx % COLS;
+        for (int idx = threadIdx.x; idx < nt * DELTA_COLS; idx += blockDim.x) {
+            const int tt = idx / DELTA_COLS, j = idx % DELTA_COLS;
             vs[tt][j] = col0 + j < V ? vv[((size_t)(c0 + tt) * H + h) * V + col0 + j] : 0.0f;
         }
         if (threadIdx.x < nt) {
@@ -178,51 +176,38 @@ delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ 
             gs[threadIdx.x] = decay[(size_t)(c0 + threadIdx.x) * H + h];
         }
         __syncthreads();
-        for (int tt = warp; tt < nt; tt += 4) {
+        for (int tt = warp; tt < nt; tt += DELTA_COLS) {
             float dot = 0.0f;
-            for (int i = lane; i < LD; i += 32)
-                if ((i % (DPT + 4)) < DPT) dot += ks[tt][i] * qs[tt][i];
+            for (int i = lane; i < LD; i += 32) dot += ks[tt][i] * qs[tt][i];
             dot = warp_sum(dot);
             if (lane == 0) kqs[tt] = dot;
         }
         __syncthreads();
         for (int tt = 0; tt < nt; ++tt) {
-            const float4* k4 = reinterpret_cast<const float4*>(&ks[tt][part * (DPT + 4)]);
-            const float4* q4 = reinterpret_cast<const float4*>(&qs[tt][part * (DPT + 4)]);
-            // four sums each, added pairwise at the end: the chain of dependent additions is a quarter as long
-            float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f, b0 = 0.0f, b1 = 0.0f, b2 = 0.0f, b3 = 0.0f;
-            float4 kv[DPT / 4];
+            float kv[DPT];
+            float a = 0.0f, b = 0.0f;
 #pragma unroll
-            for (int m = 0; m < DPT / 4; ++m) {
-                kv[m] = k4[m];
-                const float4 qv = q4[m];
-                a0 = fmaf(S[4 * m], kv[m].x, a0); a1 = fmaf(S[4 * m + 1], kv[m].y, a1);
-                a2 = fmaf(S[4 * m + 2], kv[m].z, a2); a3 = fmaf(S[4 * m + 3], kv[m].w, a3);
-                b0 = fmaf(S[4 * m], qv.x, b0); b1 = fmaf(S[4 * m + 1], qv.y, b1);
-                b2 = fmaf(S[4 * m + 2], qv.z, b2); b3 = fmaf(S[4 * m + 3], qv.w, b3);
+            for (int m = 0; m < DPT; ++m) {
+                kv[m] = ks[tt][m * 32 + lane];
+                a = fmaf(S[m], kv[m], a);
+                b = fmaf(S[m], qs[tt][m * 32 + lane], b);
             }
-            float a = (a0 + a1) + (a2 + a3), b = (b0 + b1) + (b2 + b3);
 #pragma unroll
-            for (int offset = 1; offset < LANES; offset <<= 1) {
+            for (int offset = 16; offset > 0; offset >>= 1) {
                 a += __shfl_xor_sync(0xffffffffu, a, offset);
                 b += __shfl_xor_sync(0xffffffffu, b, offset);
             }
             const float g = gs[tt];
-            const float u = bs[tt] * (vs[tt][local] - g * a);
+            const float u = bs[tt] * (vs[tt][warp] - g * a);
 #pragma unroll
-            for (int m = 0; m < DPT / 4; ++m) {
-                S[4 * m] = fmaf(kv[m].x, u, g * S[4 * m]);
-                S[4 * m + 1] = fmaf(kv[m].y, u, g * S[4 * m + 1]);
-                S[4 * m + 2] = fmaf(kv[m].z, u, g * S[4 * m + 2]);
-                S[4 * m + 3] = fmaf(kv[m].w, u, g * S[4 * m + 3]);
-            }
-            if (part == 0 && col < V) out[((size_t)(c0 + tt) * H + h) * V + col] = g * b + kqs[tt] * u;
+            for (int m = 0; m < DPT; ++m) S[m] = fmaf(kv[m], u, g * S[m]);
+            if (lane == 0 && col < V) out[((size_t)(c0 + tt) * H + h) * V + col] = g * b + kqs[tt] * u;
         }
     }
 #pragma unroll
     for (int m = 0; m < DPT; ++m) {
-        const int i = part * DPT + m;
-        if (i < D && col < V) Sg[(size_t)i * V + col] = S[m];
+        const int i = m * 32 + lane;
+        if (i < D && col < V) Sg[i] = S[m];
     }
 }
 
@@ -278,13 +263,14 @@ KB_EXPORT int kb_delta_recurrence(const float* qn, const float* kn, const float*
     if (num_rows == 0) return 0;
     if (!qn || !kn || !vv || !beta || !decay || !states || !qo_indptr || !state_slots || !out) return KB_ERR_NULL;
     if (D < 1 || D > 256 || KH < 1 || H % KH != 0 || V < 1 || H > 65535) return KB_ERR_UNSUPPORTED_SIZE;
-    dim3 grid(num_rows, H, (V + 128 / DELTA_LANES - 1) / (128 / DELTA_LANES));
+    dim3 grid(num_rows, H, (V + DELTA_COLS - 1) / DELTA_COLS);
+    const dim3 block(32 * DELTA_COLS);
     if (D <= 64)
-        kb_launch(delta_recurrence_kernel<8>, grid, dim3(128), 0, stream, qn, kn, vv, beta, decay, states, qo_indptr, state_slots, KH, D, H, V, out);
+        kb_launch(delta_recurrence_kernel<2>, grid, block, 0, stream, qn, kn, vv, beta, decay, states, qo_indptr, state_slots, KH, D, H, V, out);
     else if (D <= 128)
-        kb_launch(delta_recurrence_kernel<16>, grid, dim3(128), 0, stream, qn, kn, vv, beta, decay, states, qo_indptr, state_slots, KH, D, H, V, out);
+        kb_launch(delta_recurrence_kernel<4>, grid, block, 0, stream, qn, kn, vv, beta, decay, states, qo_indptr, state_slots, KH, D, H, V, out);
     else
-        kb_launch(delta_recurrence_kernel<32>, grid, dim3(128), 0, stream, qn, kn, vv, beta, decay, states, qo_indptr, state_slots, KH, D, H, V, out);
+        kb_launch(delta_recurrence_kernel<8>, grid, block, 0, stream, qn, kn, vv, beta, decay, states, qo_indptr, state_slots, KH, D, H, V, out);
     return kb_launch_result();
 }
 

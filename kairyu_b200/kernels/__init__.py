@@ -1306,14 +1306,14 @@ def delta_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: to
                      out: torch.Tensor, *, qo_indptr: torch.Tensor, state_slots: torch.Tensor, kv_heads: int, dim: int, heads: int,
                      vdim: int) -> None:
     """Every row's tokens in order through S <- g S + k (beta (v - g S^T k))^T, o = S^T q; ``states``
-    [slots, heads, dim, vdim] fp32 is read and left updated."""
+    [slots, heads, vdim, dim] fp32 (S column by column) is read and left updated."""
     _need_cuda("delta_recurrence", q, k, v, beta, decay, states, out, qo_indptr, state_slots)
     _need_i32("delta_recurrence", qo_indptr, state_slots)
     for tensor in (q, k, v, beta, decay, states, out):
         if tensor.dtype != torch.float32 or not tensor.is_contiguous():
             raise KernelError("delta_recurrence: contiguous fp32 tensors only")
-    if tuple(states.shape[1:]) != (heads, dim, vdim) or out.numel() != v.numel():
-        raise KernelError("delta_recurrence: the state must be [slots, heads, dim, vdim] and the output as large as v")
+    if tuple(states.shape[1:]) != (heads, vdim, dim) or out.numel() != v.numel():
+        raise KernelError("delta_recurrence: the state must be [slots, heads, vdim, dim] and the output as large as v")
     if dim > 256:
         raise KernelError(f"delta_recurrence: dim {dim} > 256 is not supported")
     fn = _fn("delta_rule", "kb_delta_recurrence",

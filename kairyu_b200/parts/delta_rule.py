@@ -97,7 +97,7 @@ class GatedDeltaRule(Mixer):
         return sum(t.numel() * t.element_size() for t in (self.w_in, self.w_gates, self.taps, self.a_log, self.dt_bias, self.out_norm, self.w_o))
 
     def cache_specs(self) -> tuple[Any, ...]:
-        specs = [StateSpec((self.num_heads, self.head_dim, self.value_dim), "float32")]
+        specs = [StateSpec((self.num_heads, self.value_dim, self.head_dim), "float32")]  # S column by column
         if self.conv_taps > 1:
             specs.append(StateSpec((self.conv_taps - 1, self.channels), "float32"))
         return tuple(specs)

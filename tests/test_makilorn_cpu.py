@@ -42,7 +42,7 @@ def test_spec_run_order_and_cache_needs(name):
         if entry["type"] == "latent_attention":
             assert needs[index] == (PagedKVSpec(1, m["kv_rank"], m["mask"]["size"], v_head_dim=0),)
         else:
-            wanted = [StateSpec((m["heads"], m["dim"], m["vdim"]), "float32")]
+            wanted = [StateSpec((m["heads"], m["vdim"], m["dim"]), "float32")]
             if m["conv"] > 1:
                 wanted.append(StateSpec((m["conv"] - 1, 2 * m["kv_heads"] * m["dim"] + m["heads"] * m["vdim"]), "float32"))
             assert needs[index] == tuple(wanted)
