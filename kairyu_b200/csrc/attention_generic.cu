@@ -14,7 +14,7 @@
 #include "common.cuh"
 
 #define ATT_WARPS 4
-#define ATT_MAX_D 512
+#define ATT_MAX_D 1024
 #define ATT_MAX_K (ATT_MAX_D / 32)
 
 template <typename T>

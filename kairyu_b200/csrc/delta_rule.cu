@@ -63,10 +63,10 @@ delta_prepare_kernel(const TA* __restrict__ proj, int stride, const float* __res
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     // q and k heads: one warp a head
     for (int unit = warp; unit < 2 * KH; unit += warps) {
-        float vals[8];
+        float vals[16];
         float ss = 0.0f;
 #pragma unroll
-        for (int m = 0; m < 8; ++m) {
+        for (int m = 0; m < 16; ++m) {
             const int e = lane + 32 * m;
             float z = 0.0f;
             if (e < D) {
@@ -87,7 +87,7 @@ delta_prepare_kernel(const TA* __restrict__ proj, int stride, const float* __res
             dst = kn + ((size_t)t * KH + (unit - KH)) * D;
         }
 #pragma unroll
-        for (int m = 0; m < 8; ++m) {
+        for (int m = 0; m < 16; ++m) {
             const int e = lane + 32 * m;
             if (e < D) dst[e] = vals[m] * scale;
         }
@@ -139,10 +139,11 @@ delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ 
                         const int* __restrict__ qo_indptr, const int* __restrict__ state_slots, int KH, int D, int H, int V,
                         float* __restrict__ out) {
     constexpr int LD = 32 * DPT;  // entries of a key or query row as staged (zeros beyond D)
-    __shared__ __align__(16) float ks[DELTA_CHUNK][LD];
-    __shared__ __align__(16) float qs[DELTA_CHUNK][LD];
-    __shared__ float vs[DELTA_CHUNK][DELTA_COLS];
-    __shared__ float bs[DELTA_CHUNK], gs[DELTA_CHUNK], kqs[DELTA_CHUNK];
+    constexpr int CHUNK = DPT <= 8 ? DELTA_CHUNK : DELTA_CHUNK / 2;  // tokens staged at a time (shared memory)
+    __shared__ __align__(16) float ks[CHUNK][LD];
+    __shared__ __align__(16) float qs[CHUNK][LD];
+    __shared__ float vs[CHUNK][DELTA_COLS];
+    __shared__ float bs[CHUNK], gs[CHUNK], kqs[CHUNK];
     const int row = blockIdx.x, h = blockIdx.y;
     const int col0 = blockIdx.z * DELTA_COLS;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -158,8 +159,8 @@ delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ 
         const int i = m * 32 + lane;
         S[m] = (i < D && col < V) ? Sg[i] : 0.0f;
     }
-    for (int c0 = t0; c0 < t1; c0 += DELTA_CHUNK) {
-        const int nt = min(DELTA_CHUNK, t1 - c0);
+    for (int c0 = t0; c0 < t1; c0 += CHUNK) {
+        const int nt = min(CHUNK, t1 - c0);
         __syncthreads();
         for (int idx = threadIdx.x; idx < nt * LD; idx += blockDim.x) {
             const int tt = idx / LD, i = idx % LD;
@@ -238,7 +239,7 @@ KB_EXPORT int kb_delta_prepare(const void* proj, int stride, int is_bf16, const 
     if (T == 0) return 0;
     if (!proj || !gates || !taps || !row_ids || !qo_indptr || !state_slots || !A_log || !dt_bias || !qn || !kn || !vv || !beta || !decay)
         return KB_ERR_NULL;
-    if (n < 1 || n > DELTA_MAX_TAPS + 1 || D < 1 || D > 256 || KH < 1 || H % KH != 0 || V < 1) return KB_ERR_UNSUPPORTED_SIZE;
+    if (n < 1 || n > DELTA_MAX_TAPS + 1 || D < 1 || D > 512 || KH < 1 || H % KH != 0 || V < 1) return KB_ERR_UNSUPPORTED_SIZE;
     if (n > 1 && !conv_state) return KB_ERR_NULL;
     const int C = 2 * KH * D + H * V;
     if (is_bf16)
@@ -262,15 +263,17 @@ KB_EXPORT int kb_delta_recurrence(const float* qn, const float* kn, const float*
                                   float* out, int num_rows, cudaStream_t stream) {
     if (num_rows == 0) return 0;
     if (!qn || !kn || !vv || !beta || !decay || !states || !qo_indptr || !state_slots || !out) return KB_ERR_NULL;
-    if (D < 1 || D > 256 || KH < 1 || H % KH != 0 || V < 1 || H > 65535) return KB_ERR_UNSUPPORTED_SIZE;
+    if (D < 1 || D > 512 || KH < 1 || H % KH != 0 || V < 1 || H > 65535) return KB_ERR_UNSUPPORTED_SIZE;
     dim3 grid(num_rows, H, (V + DELTA_COLS - 1) / DELTA_COLS);
     const dim3 block(32 * DELTA_COLS);
     if (D <= 64)
         kb_launch(delta_recurrence_kernel<2>, grid, block, 0, stream, qn, kn, vv, beta, decay, states, qo_indptr, state_slots, KH, D, H, V, out);
     else if (D <= 128)
         kb_launch(delta_recurrence_kernel<4>, grid, block, 0, stream, qn, kn, vv, beta, decay, states, qo_indptr, state_slots, KH, D, H, V, out);
-    else
+    else if (D <= 256)
         kb_launch(delta_recurrence_kernel<8>, grid, block, 0, stream, qn, kn, vv, beta, decay, states, qo_indptr, state_slots, KH, D, H, V, out);
+    else
+        kb_launch(delta_recurrence_kernel<16>, grid, block, 0, stream, qn, kn, vv, beta, decay, states, qo_indptr, state_slots, KH, D, H, V, out);
     return kb_launch_result();
 }
 

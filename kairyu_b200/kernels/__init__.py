@@ -287,8 +287,8 @@ def paged_attention_generic(
         raise KernelError("paged_attention_generic: dtype or cache shape mismatch")
     if q.stride(1) != 1 or out.stride(1) != 1 or not k_cache.is_contiguous() or not v_cache.is_contiguous():
         raise KernelError("paged_attention_generic: inner strides must be 1 and caches contiguous")
-    if head_dim > 512:
-        raise KernelError(f"paged_attention_generic: head_dim {head_dim} > 512 is not supported")
+    if head_dim > 1024:
+        raise KernelError(f"paged_attention_generic: head_dim {head_dim} > 1024 is not supported")
     if num_q_heads % num_kv_heads:
         raise KernelError("paged_attention_generic: query heads must be a multiple of KV heads")
     T = q.shape[0]
@@ -1314,8 +1314,8 @@ def delta_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: to
             raise KernelError("delta_recurrence: contiguous fp32 tensors only")
     if tuple(states.shape[1:]) != (heads, vdim, dim) or out.numel() != v.numel():
         raise KernelError("delta_recurrence: the state must be [slots, heads, vdim, dim] and the output as large as v")
-    if dim > 256:
-        raise KernelError(f"delta_recurrence: dim {dim} > 256 is not supported")
+    if dim > 512:
+        raise KernelError(f"delta_recurrence: dim {dim} > 512 is not supported")
     fn = _fn("delta_rule", "kb_delta_recurrence",
              [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p])
     _check(
