@@ -106,13 +106,15 @@ def test_every_cut_matches_plain(case, dtype, decode_mode):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("kind", ["latent", "latent_wide", "latent_many_heads", "latent_huge_rank", "delta", "delta_shared_heads", "delta_wide"])
+@pytest.mark.parametrize("kind", ["latent", "latent_wide", "latent_rank192", "latent_rank256", "latent_many_heads", "latent_huge_rank", "delta", "delta_shared_heads", "delta_wide"])
 def test_one_mixer_alone(kind, dtype, tmp_path):
     """A model of one layer without feed-forward, so that the mixer is all that mixes: a prompt of
     several windows' length in one step, then decoding over more than a window."""
     mixers = {
         "latent": latent(2, 16, 24, 48, 19, 0.5),
         "latent_wide": latent(3, 32, 32, 128, 70, 0.25),  # rank 128: the two-tile tcgen05 kernel's size
+        "latent_rank192": latent(2, 16, 16, 192, 50, 0.3),    # mma.sync prefill with the TMA decode kernel
+        "latent_rank256": latent(4, 8, 24, 256, 131, 0.3),
         "latent_many_heads": latent(19, 8, 8, 64, 45, 0.4),  # more heads than one attention call takes
         "latent_huge_rank": latent(2, 8, 8, 520, 33, 0.3),   # wider than any tensor-core kernel's rows
         "delta_wide": delta(1, 1, 288, 8, 2),               # the widest variant of the recurrence
