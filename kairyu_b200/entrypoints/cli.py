@@ -150,7 +150,7 @@ def _validate(args: argparse.Namespace) -> int:
     except Exception as error:  # report, do not trace
         print(f"invalid: {error}")
         return 1
-    print(f"valid: {parsed.architecture}, {parsed.num_hidden_layers} layers, {len(specs)} tensors")
+    print(f"valid: {parsed.architecture}, {len(model.schedule)} layers, {len(specs)} tensors")
     return 0
 
 

@@ -1,0 +1,146 @@
+"""Plain torch statements of the kernels that Makilorn's parts call, with the signatures of
+``kairyu_b200.kernels``, for CPU runs of the cache manager, the step function, the scheduler and
+the command line (32-bit only).  ``install`` puts them, and those of ``torch_kernels``, in place of
+the kernels for one test.  They are test code: the package has no implementation but its kernels."""
+
+from __future__ import annotations
+
+import torch
+
+import torch_kernels
+
+
+def output_norm_add(residual, y, weight, eps, copy):
+    import kairyu_b200.kernels as kernels
+
+    if isinstance(y, kernels.WeightedRows):
+        tokens, top = y.weights.shape
+        rows = y.rows.float() if y.at is None else y.rows.float()[y.at.long()]
+        y = (rows.view(tokens, top, -1) * y.weights.unsqueeze(-1)).sum(1)
+    y = y.float()
+    residual.add_(y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + eps) * weight.float())
+    if copy is not None:
+        copy.copy_(residual.to(copy.dtype))
+
+
+def residual_copy(residual, copy):
+    copy.copy_(residual.to(copy.dtype))
+
+
+def latent_norm_write(packed, offset, rank, weight, eps, cache, *, positions, row_ids, block_table, write_from, flag=None):
+    z = packed[:, offset : offset + rank].float()
+    c = z * torch.rsqrt(z.pow(2).mean(-1, keepdim=True) + eps) * weight.float()
+    page_size = cache.shape[1]
+    for t in range(packed.shape[0]):
+        position, row = int(positions[t]), int(row_ids[t])
+        if write_from is not None and position < int(write_from[row]):
+            continue
+        page = int(block_table[row, position // page_size])
+        assert 0 <= page < cache.shape[0]
+        cache[page, position % page_size, 0] = c[t].to(cache.dtype)
+
+
+def heads_linear(x, weight, out):
+    out.copy_(torch.einsum("thk,hnk->thn", x.float(), weight.float()).to(out.dtype))
+
+
+def delta_prepare(packed, gates, taps, conv_state, *, row_ids, qo_indptr, state_slots, a_log, dt_bias, kv_heads, dim, heads, vdim,
+                  q, k, v, beta, decay, flag=None):
+    n = taps.shape[1]
+    channels = 2 * kv_heads * dim + heads * vdim
+    tokens = packed.shape[0]
+    conv = torch.zeros(tokens, channels)
+    for row in range(qo_indptr.numel() - 1):
+        t0, t1 = int(qo_indptr[row]), int(qo_indptr[row + 1])
+        slot = int(state_slots[row])
+        inputs = packed[t0:t1, :channels].float()
+        if n > 1:
+            history = torch.cat([conv_state[slot], inputs], dim=0)  # the kept inputs, then the step's
+            conv_state[slot] = history[-(n - 1) :]
+        else:
+            history = inputs
+        for index in range(t1 - t0):
+            window = history[index : index + n]  # inputs at offsets -(n-1) .. 0 of this token
+            conv[t0 + index] = (window * taps.t()).sum(0)
+    act = conv / (1.0 + torch.exp(-conv))
+    qk = kv_heads * dim
+    qh = act[:, :qk].view(tokens, kv_heads, dim)
+    kh = act[:, qk : 2 * qk].view(tokens, kv_heads, dim)
+    q.view(tokens, kv_heads, dim).copy_(qh * torch.rsqrt(qh.pow(2).sum(-1, keepdim=True) + 1e-6) * dim ** -0.5)
+    k.view(tokens, kv_heads, dim).copy_(kh * torch.rsqrt(kh.pow(2).sum(-1, keepdim=True) + 1e-6))
+    v.view(tokens, heads * vdim).copy_(act[:, 2 * qk :])
+    beta.copy_(torch.sigmoid(gates[:, :heads]))
+    decay.copy_(torch.exp(-torch.exp(a_log) * torch.nn.functional.softplus(gates[:, heads:] + dt_bias)))
+
+
+def delta_recurrence(q, k, v, beta, decay, states, out, *, qo_indptr, state_slots, kv_heads, dim, heads, vdim):
+    tokens = q.shape[0]
+    q, k = q.view(tokens, kv_heads, dim), k.view(tokens, kv_heads, dim)
+    v, out = v.view(tokens, heads, vdim), out.view(tokens, heads, vdim)
+    for row in range(qo_indptr.numel() - 1):
+        slot = int(state_slots[row])
+        for h in range(heads):
+            S = states[slot, h].t().clone()  # stored column by column: [vdim, dim]
+            for t in range(int(qo_indptr[row]), int(qo_indptr[row + 1])):
+                kt, qt = k[t, h // (heads // kv_heads)], q[t, h // (heads // kv_heads)]
+                S = decay[t, h] * S
+                u = beta[t, h] * (v[t, h] - S.t() @ kt)
+                S = S + torch.outer(kt, u)
+                out[t, h] = S.t() @ qt
+            states[slot, h] = S.t()
+
+
+def delta_gated_norm(o, packed, gate_offset, weight, eps, out, *, heads, vdim):
+    tokens = packed.shape[0]
+    o = o.view(tokens, heads, vdim)
+    gate = packed[:, gate_offset : gate_offset + heads * vdim].float().view(tokens, heads, vdim)
+    normed = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + eps) * weight * (gate / (1.0 + torch.exp(-gate)))
+    out.copy_(normed.reshape(tokens, heads * vdim).to(out.dtype))
+
+
+def moe_route(logits, bias, top, ids, weights):
+    z = logits + (bias.float() if bias is not None else 0.0)
+    for t in range(z.shape[0]):
+        chosen = sorted(range(z.shape[1]), key=lambda e: (-float(z[t, e]), e))[:top]
+        ids[t] = torch.tensor(chosen, dtype=torch.int32)
+        weights[t] = torch.softmax(z[t, chosen], dim=0)
+
+
+def moe_plan(ids, experts, plan):
+    top = ids.shape[1]
+    flat = ids.reshape(-1).tolist()
+    order = sorted(range(len(flat)), key=lambda p: (flat[p], p))
+    return {"sorted": order, "experts": flat, "top": top}
+
+
+def moe_grouped(a, weight, out, plan, *, top, gated, limit=0.0, alpha=1.702):
+    for place, pair in enumerate(plan["sorted"]):
+        w = weight[plan["experts"][pair]].float()
+        if gated:
+            both = w @ a[pair // top].float()
+            half = both.shape[0] // 2
+            g = both[:half].clamp(max=limit)
+            u = both[half:].clamp(min=-limit, max=limit)
+            out[place] = (g * torch.sigmoid(alpha * g) * (u + 1.0)).to(out.dtype)
+        else:
+            out[pair] = w @ a[place].float()
+
+
+def moe_combine(rows, weights, out, at=None):
+    tokens, top = weights.shape
+    picked = rows.float() if at is None else rows.float()[at.long()]
+    out.copy_((picked.view(tokens, top, -1) * weights.unsqueeze(-1)).sum(1).to(out.dtype))
+
+
+_NAMES = [
+    "output_norm_add", "residual_copy", "latent_norm_write", "heads_linear", "delta_prepare", "delta_recurrence", "delta_gated_norm",
+    "moe_route", "moe_plan", "moe_grouped", "moe_combine",
+]
+
+
+def install(monkeypatch) -> None:
+    import kairyu_b200.kernels as kernels
+
+    torch_kernels.install(monkeypatch)
+    for name in _NAMES:
+        monkeypatch.setattr(kernels, name, globals()[name])

@@ -144,3 +144,77 @@ def test_plain_model_pieces():
     longer["layers"][1]["mixer"]["mask"]["size"] = 500
     assert torch.allclose(plain.forward(long_window, weights, tokens), plain.forward(longer, weights, tokens), atol=1e-9)
     assert not torch.allclose(plain.forward(cfg, weights, tokens), plain.forward(longer, weights, tokens), atol=1e-3)
+
+
+# ---------------------------------------------------------------------------- the engine on the CPU
+# The kernels replaced by their torch statements (makilorn_torch_kernels.py): the cache manager's
+# windowed groups and state slots, the step function, the scheduler and the command line as this
+# design drives them, in 32-bit.  The same workloads run on the GPU with the kernels.
+
+SHORT = [33, 12, 40, 9, 2, 1, 27]
+
+
+def cpu_runner(folder, *, page_size, num_pages, max_requests=4):
+    from kairyu_b200.cache import CacheManager, CacheStorage
+    from kairyu_b200.engine.engine import load_model
+    from kairyu_b200.engine.runner import ModelRunner
+
+    model, _ = load_model(folder, dtype="float32", device="cpu")
+    layout = CacheLayout.from_slot_specs(model.cache_slot_specs())
+    cache = CacheManager(layout, num_pages=num_pages, page_size=page_size, max_requests=max_requests)
+    storage = CacheStorage(layout, num_pages=num_pages, page_size=page_size, max_requests=max_requests, dtype=model.dtype, device="cpu")
+    return ModelRunner(model, cache, storage, max_model_len=512, decode_mode="eager", check_tables=True, debug_poison=True)
+
+
+@pytest.mark.parametrize("name", ["mixed", "rank32"])
+def test_every_cut_on_the_cpu(name, tmp_path, monkeypatch):
+    import makilorn_torch_kernels
+
+    makilorn_torch_kernels.install(monkeypatch)
+    cfg, seed, page_size = CASES[name]
+    weights = make_weights(cfg, seed)
+    folder = write_model(cfg, weights, tmp_path / "m")
+    requests = traces.make_requests(cfg["vocab"], SHORT, seed=3)
+    expected = {n: plain.forward(cfg, weights, t, dtype=torch.float64).numpy() for n, t in requests.items()}
+    cuts = {
+        "whole": traces.trace_whole(requests),
+        "tail": traces.trace_decode_tail(requests, 6),
+        "chunks": traces.trace_chunks(requests, sizes=(5, 2, 11, 3)),
+        "mixed": traces.trace_mixed(requests, seed=4, max_live=3),
+    }
+    pool = max(traces.peak_tokens(steps, round_to=page_size) for steps in cuts.values()) // page_size + 1
+    runner = cpu_runner(folder, page_size=page_size, num_pages=pool, max_requests=3)  # three slots for seven requests
+    for cut, steps in cuts.items():
+        result = traces.run_in_process(runner, steps)
+        assert len(result) == sum(SHORT)
+        worst = max(relative_error(row, expected[n][p]) for (n, p), row in result.items())
+        assert worst < 1e-4, (cut, worst)
+        assert runner.cache.live_requests == 0
+
+
+def test_generation_and_the_command_line_on_the_cpu(tmp_path, capsys, monkeypatch):
+    """make-random, validate, generate: greedy tokens through the scheduler (a token budget that cuts the
+    prompts) equal the plain model's own continuation."""
+    import makilorn_torch_kernels
+    from safetensors.torch import load_file
+
+    from kairyu_b200.entrypoints import cli
+
+    makilorn_torch_kernels.install(monkeypatch)
+    cfg = CASES["mixed"][0]
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    folder = tmp_path / "model"
+    cli.main(["make-random", str(tmp_path / "config.json"), str(folder), "--seed", "5", "--dtype", "float32"])
+    cli.main(["validate", str(folder)])
+    assert "valid: Makilorn, 5 layers" in capsys.readouterr().out
+    prompts = [[5, 17, 3, 9], [1], list(range(20, 60))]
+    cli.main(["generate", str(folder), "--dtype", "float32", "--device", "cpu", "--temperature", "0", "--max-tokens", "6", "--num-pages", "24",
+              "--page-size", "8", "--max-num-seqs", "2", "--max-num-batched-tokens", "16"]
+             + [arg for p in prompts for arg in ("--prompt-token-ids", ",".join(map(str, p)))])
+    lines = [json.loads(line) for line in capsys.readouterr().out.splitlines() if line.startswith("{")]
+    weights = {n: t.float() for n, t in load_file(str(folder / "model.safetensors")).items()}
+    for prompt, line in zip(prompts, lines):
+        tokens = list(prompt)
+        for _ in range(6):
+            tokens.append(int(plain.forward(cfg, weights, tokens)[-1].argmax()))
+        assert line["outputs"][0]["token_ids"] == tokens[len(prompt):]
