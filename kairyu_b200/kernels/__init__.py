@@ -1317,10 +1317,11 @@ def delta_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: to
     if dim > 512:
         raise KernelError(f"delta_recurrence: dim {dim} > 512 is not supported")
     fn = _fn("delta_rule", "kb_delta_recurrence",
-             [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p])
+             [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p])
+    rows = qo_indptr.numel() - 1
     _check(
         fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), beta.data_ptr(), decay.data_ptr(), states.data_ptr(), qo_indptr.data_ptr(),
-           state_slots.data_ptr(), kv_heads, dim, heads, vdim, out.data_ptr(), qo_indptr.numel() - 1, _stream()),
+           state_slots.data_ptr(), kv_heads, dim, heads, vdim, out.data_ptr(), rows, 1 if q.shape[0] == rows else 0, _stream()),
         "delta_recurrence",
     )
 
