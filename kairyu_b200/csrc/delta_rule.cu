@@ -9,9 +9,9 @@
 // q/k head h / (H / KH).  The output is o / rms(o) * w * silu(gate) per head.
 //
 // Four kernels:
-//   delta_prepare     per token: convolution (reaching into the request's kept inputs for the taps
-//                     that lie before the step's first token), silu, unit norms, beta and g; all
-//                     results 32-bit
+//   delta_prepare     per token and head (a warp each): convolution (reaching into the request's kept
+//                     inputs for the taps that lie before the step's first token), silu, unit norms;
+//                     beta and g per token; all results 32-bit
 //   delta_conv_state  per request: the last (taps - 1) inputs of the step become the kept inputs
 //   delta_recurrence  per (request, head, 16 columns of S): walks the request's tokens in order.
 //                     Columns of S are independent of one another, so the grid spreads them: sixteen
@@ -43,7 +43,9 @@ __device__ __forceinline__ float conv_input(const TA* __restrict__ proj, int str
     return kept[(size_t)((n - 1) + (o - back)) * C + c];
 }
 
-template <typename TA>
+// NT: the number of taps where it is one of the usual few (the taps' loop unrolls, the rows of the last
+// tokens are looked up once a token, a channel's taps come in one load); 0: any number, taken at run time.
+template <typename TA, int NT>
 __global__ void __launch_bounds__(128)
 delta_prepare_kernel(const TA* __restrict__ proj, int stride, const float* __restrict__ gates, const float* __restrict__ taps,
                      int n, const float* __restrict__ conv_state, const int* __restrict__ row_ids,
@@ -62,19 +64,47 @@ delta_prepare_kernel(const TA* __restrict__ proj, int stride, const float* __res
     const int C = 2 * KH * D + H * V;
     const float* kept = conv_state + (size_t)state_slots[row] * (n - 1) * C;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-    // q and k heads: one warp a head
-    for (int unit = warp; unit < 2 * KH; unit += warps) {
+    // where the inputs `back` tokens before this one lie: in the step's rows, or among the request's kept inputs
+    constexpr int ROWS = NT ? NT : 1;
+    const TA* step_row[ROWS];
+    const float* kept_row[ROWS];
+#pragma unroll
+    for (int back = 0; back < ROWS; ++back) {
+        step_row[back] = o - back >= 0 ? proj + (size_t)(t - back) * stride : nullptr;
+        kept_row[back] = o - back >= 0 ? nullptr : kept + (size_t)((n - 1) + (o - back)) * C;
+    }
+    auto convolve = [&](int c) -> float {
+        float z = 0.0f;
+        if constexpr (NT == 0) {
+            for (int back = 0; back < n; ++back) z += taps[(size_t)c * n + (n - 1 - back)] * conv_input(proj, stride, kept, C, n, t, o, back, c);
+        } else {
+            float w[NT];
+            if constexpr (NT == 4) {
+                const float4 all = *reinterpret_cast<const float4*>(taps + (size_t)c * 4);
+                w[0] = all.x; w[1] = all.y; w[2] = all.z; w[3] = all.w;
+            } else {
+#pragma unroll
+                for (int j = 0; j < NT; ++j) w[j] = taps[(size_t)c * NT + j];
+            }
+#pragma unroll
+            for (int back = 0; back < NT; ++back) {
+                const float x = step_row[back] ? to_float(step_row[back][c]) : kept_row[back][c];
+                z = fmaf(w[NT - 1 - back], x, z);
+            }
+        }
+        return z;
+    };
+    // A warp takes one head: of q, of k (with the unit norm) or of v; blockIdx.y spreads a token's heads over
+    // blocks, so that a step of few tokens still fills the device and no thread walks many channels in turn.
+    const int unit = blockIdx.y * warps + warp;
+    if (unit < 2 * KH) {
         float vals[16];
         float ss = 0.0f;
 #pragma unroll
         for (int m = 0; m < 16; ++m) {
             const int e = lane + 32 * m;
             float z = 0.0f;
-            if (e < D) {
-                const int c = unit * D + e;
-                for (int back = 0; back < n; ++back) z += taps[(size_t)c * n + (n - 1 - back)] * conv_input(proj, stride, kept, C, n, t, o, back, c);
-                z = silu_f(z);
-            }
+            if (e < D) z = silu_f(convolve(unit * D + e));
             vals[m] = z;
             ss += z * z;
         }
@@ -92,15 +122,11 @@ delta_prepare_kernel(const TA* __restrict__ proj, int stride, const float* __res
             const int e = lane + 32 * m;
             if (e < D) dst[e] = vals[m] * scale;
         }
+    } else if (unit < 2 * KH + H) {
+        const int first = (unit - 2 * KH) * V;
+        for (int e = lane; e < V; e += 32) vv[(size_t)t * H * V + first + e] = silu_f(convolve(2 * KH * D + first + e));
     }
-    // v channels
-    for (int i = threadIdx.x; i < H * V; i += blockDim.x) {
-        const int c = 2 * KH * D + i;
-        float z = 0.0f;
-        for (int back = 0; back < n; ++back) z += taps[(size_t)c * n + (n - 1 - back)] * conv_input(proj, stride, kept, C, n, t, o, back, c);
-        vv[(size_t)t * H * V + i] = silu_f(z);
-    }
-    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+    for (int h = threadIdx.x; blockIdx.y == 0 && h < H; h += blockDim.x) {
         const float b = gates[(size_t)t * 2 * H + h];
         const float a = gates[(size_t)t * 2 * H + H + h] + dt_bias[h];
         const float softplus = a > 20.0f ? a : log1pf(expf(a));
@@ -299,12 +325,17 @@ KB_EXPORT int kb_delta_prepare(const void* proj, int stride, int is_bf16, const 
     if (n < 1 || n > DELTA_MAX_TAPS + 1 || D < 1 || D > 512 || KH < 1 || H % KH != 0 || V < 1) return KB_ERR_UNSUPPORTED_SIZE;
     if (n > 1 && !conv_state) return KB_ERR_NULL;
     const int C = 2 * KH * D + H * V;
-    if (is_bf16)
-        kb_launch(delta_prepare_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, stream, (const __nv_bfloat16*)proj, stride, gates, taps, n,
-                  (const float*)conv_state, row_ids, qo_indptr, state_slots, A_log, dt_bias, KH, D, H, V, qn, kn, vv, beta, decay, num_rows, flag);
-    else
-        kb_launch(delta_prepare_kernel<float>, dim3(T), dim3(128), 0, stream, (const float*)proj, stride, gates, taps, n,
-                  (const float*)conv_state, row_ids, qo_indptr, state_slots, A_log, dt_bias, KH, D, H, V, qn, kn, vv, beta, decay, num_rows, flag);
+#define LAUNCH(TA, NT)                                                                                                        \
+    kb_launch(delta_prepare_kernel<TA, NT>, dim3(T, (2 * KH + H + 3) / 4), dim3(128), 0, stream, (const TA*)proj, stride, gates, taps, n,              \
+              (const float*)conv_state, row_ids, qo_indptr, state_slots, A_log, dt_bias, KH, D, H, V, qn, kn, vv, beta, decay, num_rows, flag)
+#define PICK(TA)                                                                                                              \
+    do {                                                                                                                      \
+        if (n == 1) LAUNCH(TA, 1); else if (n == 2) LAUNCH(TA, 2); else if (n == 3) LAUNCH(TA, 3); else if (n == 4) LAUNCH(TA, 4); \
+        else LAUNCH(TA, 0);                                                                                                   \
+    } while (0)
+    if (is_bf16) PICK(__nv_bfloat16); else PICK(float);
+#undef PICK
+#undef LAUNCH
     int code = kb_launch_result();
     if (code != 0 || n == 1) return code;
     dim3 grid(num_rows, (C + 127) / 128);
