@@ -58,6 +58,13 @@ CASES: dict[str, tuple[dict, int, int]] = {
         layer(delta(2, 1, 72, 48, 5), moe(4, 3, 48, 2.0)),
         layer(latent(5, 8, 8, 64, 9, 0.7), None),
     ]), 12, 16),
+    # nothing a multiple of 8: rows that start on no 16-byte boundary, the scalar paths of every kernel
+    "odd": (config(50, 77, [
+        layer(latent(3, 10, 14, 36, 13, 0.4), moe(3, 2, 18, 1.5)),
+        layer(delta(3, 1, 20, 12, 3), moe(5, 3, 10, 2.5)),
+        layer(delta(2, 2, 36, 6, 4), None),
+        layer(latent(3, 10, 14, 36, 13, 0.4), moe(3, 2, 18, 1.5), weights_of=0),
+    ]), 14, 16),
     # rank 32, pages of 4: the mma.sync attention pair; a convolution of one tap (no kept inputs);
     # one expert of one; a window of one (a token sees itself alone)
     "rank32": (config(32, 61, [
