@@ -319,6 +319,117 @@ moe_grouped_kernel(const T* __restrict__ A, int lda, const int* __restrict__ sor
     }
 }
 
+// ------------------------------------------------------------------ few pairs an expert: the weights stream
+// A decode step gives an expert a handful of tokens, and what counts is how fast its weight rows stream.
+// Here the weight rows are the M side of the mma (16 rows a warp, 64 a block) and up to 8 pairs the N side, so no
+// tensor-core work is spent on rows that are not there.  A lane fetches 16 bytes of two weight rows straight
+// from global memory (a row gives 128 contiguous bytes per step) and 16 bytes of its pair's row from shared
+// memory; the sum over k is taken in a permuted order that both operands share (columns tg*8+4j+{0..3} of a
+// 32-column run feed the j-th mma), so no data is shuffled.  The next step's loads are issued before this
+// step's products.  More than 8 pairs of a tile go in turns of 8 (the weights come from the L2 the second time).
+#define SK_PAIRS 8
+#define SK_FEATURES 64
+
+template <bool GATED>
+__global__ void __launch_bounds__(128)
+moe_skinny_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int* __restrict__ sorted, int top,
+                  const __nv_bfloat16* __restrict__ W, int N, int Kd, int Kp, const int* __restrict__ tile_expert,
+                  const int* __restrict__ tile_first, const int* __restrict__ tile_pairs, const int* __restrict__ num_tiles,
+                  float limit, float alpha, void* __restrict__ out) {
+    extern __shared__ __align__(16) unsigned char sk_shared[];
+    __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(sk_shared);  // [SK_PAIRS][Kp + 32]
+    constexpr int NB = GATED ? 2 : 1;
+    const int ldx = Kp + 32;  // rows fall on alternate halves of a 128-byte line: 16-byte reads of 8 rows do not collide
+    pdl_wait();
+    const int tile = blockIdx.x;
+    if (tile >= *num_tiles) return;
+    const int expert = tile_expert[tile], first = tile_first[tile], rows = tile_pairs[tile];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, tg = lane & 3;
+    const int f0 = blockIdx.y * SK_FEATURES + warp * 16;
+    const int r0 = f0 + g, r1 = f0 + g + 8;
+    const __nv_bfloat16* We = W + (size_t)expert * NB * N * Kd;
+    // rows beyond N read row 0 (their results are dropped)
+    const __nv_bfloat16* w0[NB];
+    const __nv_bfloat16* w1[NB];
+#pragma unroll
+    for (int b = 0; b < NB; ++b) {
+        w0[b] = We + ((size_t)b * N + (r0 < N ? r0 : 0)) * Kd;
+        w1[b] = We + ((size_t)b * N + (r1 < N ? r1 : 0)) * Kd;
+    }
+    const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+    for (int sub = 0; sub < rows; sub += SK_PAIRS) {
+        const int np = min(SK_PAIRS, rows - sub);
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < SK_PAIRS * (Kp / 8); idx += blockDim.x) {
+            const int i = idx / (Kp / 8), c = (idx % (Kp / 8)) * 8;
+            uint4 v = zero4;
+            if (i < np && c < Kd) {
+                const int place = first + sub + i;
+                const int src = GATED ? sorted[place] / top : place;
+                v = *reinterpret_cast<const uint4*>(A + (size_t)src * lda + c);
+            }
+            *reinterpret_cast<uint4*>(xs + (size_t)i * ldx + c) = v;
+        }
+        __syncthreads();
+        float acc[NB][4];
+#pragma unroll
+        for (int b = 0; b < NB; ++b)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[b][c] = 0.0f;
+        uint4 lo[NB][2], hi[NB][2], nlo[NB][2], nhi[NB][2];
+        auto fetch = [&](int kc, uint4 (&dlo)[NB][2], uint4 (&dhi)[NB][2]) {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int col = kc + half * 32 + tg * 8;
+#pragma unroll
+                for (int b = 0; b < NB; ++b) {
+                    dlo[b][half] = col < Kd ? __ldg(reinterpret_cast<const uint4*>(w0[b] + col)) : zero4;
+                    dhi[b][half] = col < Kd ? __ldg(reinterpret_cast<const uint4*>(w1[b] + col)) : zero4;
+                }
+            }
+        };
+        fetch(0, lo, hi);
+        for (int kc = 0; kc < Kp; kc += 64) {
+            if (kc + 64 < Kp) fetch(kc + 64, nlo, nhi);
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const uint4 x = *reinterpret_cast<const uint4*>(xs + (size_t)g * ldx + kc + half * 32 + tg * 8);
+                const uint32_t b0[2] = {x.x, x.y}, b1[2] = {x.z, x.w};
+#pragma unroll
+                for (int b = 0; b < NB; ++b) {
+                    const uint32_t a0[4] = {lo[b][half].x, hi[b][half].x, lo[b][half].y, hi[b][half].y};
+                    const uint32_t a1[4] = {lo[b][half].z, hi[b][half].z, lo[b][half].w, hi[b][half].w};
+                    mma_bf16_16816(acc[b], a0, b0);
+                    mma_bf16_16816(acc[b], a1, b1);
+                }
+            }
+            if (kc + 64 < Kp) {
+#pragma unroll
+                for (int b = 0; b < NB; ++b)
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        lo[b][half] = nlo[b][half];
+                        hi[b][half] = nhi[b][half];
+                    }
+            }
+        }
+        // lane (g, tg) holds features r0 (c 0, 1) and r1 (c 2, 3) of pairs 2 tg and 2 tg + 1
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int feature = c < 2 ? r0 : r1;
+            const int i = 2 * tg + (c & 1);
+            if (feature >= N || i >= np) continue;
+            const int place = first + sub + i;
+            if constexpr (GATED)
+                reinterpret_cast<__nv_bfloat16*>(out)[(size_t)place * N + feature] =
+                    __float2bfloat16_rn(expert_activation(acc[0][c], acc[NB - 1][c], limit, alpha));
+            else
+                reinterpret_cast<float*>(out)[(size_t)sorted[place] * N + feature] = acc[0][c];
+        }
+    }
+}
+
 template <typename TR, typename TO>
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const TR* __restrict__ rows, const float* __restrict__ weights, const int* __restrict__ at, int K, int H,
@@ -389,6 +500,28 @@ KB_EXPORT int kb_moe_grouped(const void* A, int lda, const int* sorted, int top,
         if (gated) LAUNCH(float, true); else LAUNCH(float, false);
     }
 #undef LAUNCH
+    return kb_launch_result();
+}
+
+KB_EXPORT int kb_moe_skinny(const void* A, int lda, const int* sorted, int top, const void* W, int N, int Kd, int gated,
+                            const int* tile_expert, const int* tile_first, const int* tile_pairs, const int* num_tiles,
+                            int max_tiles, float limit, float alpha, void* out, cudaStream_t stream) {
+    if (max_tiles == 0) return 0;
+    if (!A || !sorted || !W || !tile_expert || !tile_first || !tile_pairs || !num_tiles || !out) return KB_ERR_NULL;
+    if (N < 1 || Kd < 8 || top < 1 || Kd % 8 != 0 || lda % 8 != 0 || ((uintptr_t)A % 16) != 0 || ((uintptr_t)W % 16) != 0) return KB_ERR_BAD_ARG;
+    const int Kp = (Kd + 63) / 64 * 64;
+    const size_t smem = (size_t)SK_PAIRS * (Kp + 32) * sizeof(__nv_bfloat16);
+    if (smem > 200 * 1024) return KB_ERR_UNSUPPORTED_SIZE;
+    dim3 grid(max_tiles, (N + SK_FEATURES - 1) / SK_FEATURES);
+    if (gated) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(moe_skinny_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        kb_launch(moe_skinny_kernel<true>, grid, dim3(128), smem, stream, (const __nv_bfloat16*)A, lda, sorted, top, (const __nv_bfloat16*)W, N, Kd, Kp,
+                  tile_expert, tile_first, tile_pairs, num_tiles, limit, alpha, out);
+    } else {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(moe_skinny_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        kb_launch(moe_skinny_kernel<false>, grid, dim3(128), smem, stream, (const __nv_bfloat16*)A, lda, sorted, top, (const __nv_bfloat16*)W, N, Kd, Kp,
+                  tile_expert, tile_first, tile_pairs, num_tiles, limit, alpha, out);
+    }
     return kb_launch_result();
 }
 

@@ -1440,6 +1440,41 @@ def moe_grouped(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, plan: 
               plan["max_tiles"], float(limit), float(alpha), out.data_ptr(), _stream()), "moe_grouped")
 
 
+# The few-pairs kernel is taken for up to this many tokens a step, in models this narrow: measured against the
+# library's grouped product (32 experts, 4 a token; gate/up + down, microseconds with about 17 of overhead in each
+# figure): width 2,048 and 1,024 rows an expert 53+33 / 65+38 / 69+44 / 77+52 against 52+41 / 69+51 / 78+57 / 87+65 at
+# 1 / 4 / 8 / 16 tokens; at width 4,096 and 2,048 rows an expert it is behind at every size (132+60 against 64+46 at
+# one token: four experts are 128 blocks of a megabyte each, too few loads in flight), and at 64 tokens everywhere.
+MOE_SKINNY_MAX_TOKENS = 16
+MOE_SKINNY_MAX_WIDTH = 2048
+
+
+def moe_skinny_ok(tokens: int, hidden: int, intermediate: int, dtype: torch.dtype) -> bool:
+    """Whether a step's experts run on the weight-streaming kernel for few pairs an expert: bfloat16, rows of whole
+    16 bytes, a decode-sized step of a narrow model."""
+    return (dtype == torch.bfloat16 and tokens <= MOE_SKINNY_MAX_TOKENS and hidden % 8 == 0 and intermediate % 8 == 0
+            and max(hidden, intermediate) <= MOE_SKINNY_MAX_WIDTH)
+
+
+def moe_skinny(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, plan: dict, *, top: int, gated: bool, limit: float = 0.0,
+               alpha: float = 1.702) -> None:
+    """``moe_grouped`` for few pairs an expert (bfloat16): the weight rows are the tensor cores' M side, up to 8
+    pairs at a time the N side, and the weights are read straight from global memory.  Same operands and results."""
+    _need_cuda("moe_skinny", a, weight, out)
+    experts, rows, K = weight.shape
+    N = rows // 2 if gated else rows
+    pairs = plan["sorted"].numel()
+    if a.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or a.shape[1] != K or a.stride(1) != 1 or not weight.is_contiguous() or not out.is_contiguous():
+        raise KernelError("moe_skinny: bfloat16 operands of one K, the weight and the output contiguous")
+    if out.shape != (pairs, N) or out.dtype != (torch.bfloat16 if gated else torch.float32):
+        raise KernelError("moe_skinny: the output does not fit")
+    fn = _fn("moe", "kb_moe_skinny", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                       c_void_p, c_int, c_float, c_float, c_void_p, c_void_p])
+    _check(fn(a.data_ptr(), a.stride(0), plan["sorted"].data_ptr(), int(top), weight.data_ptr(), N, K, 1 if gated else 0,
+              plan["tile_expert"].data_ptr(), plan["tile_first"].data_ptr(), plan["tile_pairs"].data_ptr(), plan["num_tiles"].data_ptr(),
+              plan["max_tiles"], float(limit), float(alpha), out.data_ptr(), _stream()), "moe_skinny")
+
+
 def moe_combine(rows: torch.Tensor, weights: torch.Tensor, out: torch.Tensor, at: Optional[torch.Tensor] = None) -> None:
     """out[t] = sum_k weights[t, k] * rows[t * K + k] (or rows[at[t * K + k]]): fp32 sum, in the order of k."""
     _need_cuda("moe_combine", rows, weights, out, at)

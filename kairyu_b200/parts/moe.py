@@ -7,7 +7,9 @@ the weights are the softmax over the chosen logits only.  An expert is
 ``b = clamp(W_up x, -limit, limit)``.
 
 A step's (token, expert) pairs are sorted by expert on the device (``csrc/moe.cu``).  In bfloat16
-with rows of whole 16 bytes the two products of the experts go to the library's grouped product,
+with rows of whole 16 bytes a step of up to 16 tokens runs the weight-streaming kernel for few pairs
+an expert (gate and up with the activation in the epilogue, then down), and a larger step hands
+the two products of the experts to the library's grouped product,
 which reads the group sizes on the device, with a gather before, the experts' activation between
 and the rows left in sorted order; float32 and other sizes run this package's own grouped kernels
 (gate and up with the activation in the epilogue, then down).  Nothing comes back to the host, so
@@ -102,7 +104,14 @@ class MixtureOfExperts(FeedForward):
         kernels.moe_route(logits, self.b_router, top, ids, weights)
         pairs = tokens * top
         plan = kernels.moe_plan(ids, experts, ws.flat("moe.plan", kernels.moe_plan_size(pairs, experts), torch.int32))
-        if kernels.moe_library_products_ok(self.hidden_size, self.intermediate_size, self.dtype):
+        if kernels.moe_skinny_ok(tokens, self.hidden_size, self.intermediate_size, self.dtype):
+            # a decode-sized step: an expert has a handful of pairs and its weights stream once (gate and up with the
+            # activation in the epilogue, then down)
+            hidden = ws.buffer("moe.hidden", pairs, self.intermediate_size, self.dtype)
+            kernels.moe_skinny(x, self.w_gate_up, hidden, plan, top=top, gated=True, limit=self.limit, alpha=self.alpha)
+            rows, at = ws.buffer("moe.rows", pairs, self.hidden_size, torch.float32), None
+            kernels.moe_skinny(hidden, self.w_down, rows, plan, top=top, gated=False)
+        elif kernels.moe_library_products_ok(self.hidden_size, self.intermediate_size, self.dtype):
             # bfloat16, aligned sizes: the tokens' rows are laid out run by run and the library's grouped
             # product (group sizes read on the device) runs both products; the rows stay in that order
             gathered = ws.buffer("moe.gathered", pairs, self.hidden_size, self.dtype)

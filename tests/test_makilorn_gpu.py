@@ -133,11 +133,12 @@ def test_one_mixer_alone(kind, dtype, tmp_path):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("sizes", [(40, 5, 2, 24, 1.25, 33), (64, 8, 8, 16, 0.5, 3), (24, 1, 1, 70, 2.0, 130), (96, 16, 3, 96, 1.5, 700), (40, 6, 2, 20, 1.0, 300)])
+@pytest.mark.parametrize("sizes", [(40, 5, 2, 24, 1.25, 33), (64, 8, 8, 16, 0.5, 3), (72, 4, 2, 40, 1.5, 16), (136, 3, 1, 200, 2.0, 11), (24, 1, 1, 70, 2.0, 130), (96, 16, 3, 96, 1.5, 700), (40, 6, 2, 20, 1.0, 300)])
 def test_mixture_of_experts_alone(sizes, dtype):
     """The part by itself, rows summed here (``combine=True``) and handed on weighted.  Sizes whose rows
-    are whole 16 bytes take the library's grouped product in bfloat16, the others (70 and 20 rows an
-    expert) this package's tensor-core kernel; float32 always takes the FMA kernel."""
+    are whole 16 bytes take, in bfloat16, the few-pairs kernel up to 16 tokens (one case with all 16 tokens
+    on few experts: more than 8 pairs a tile) and the library's grouped product beyond; the others (70 and
+    20 rows an expert) this package's tiled tensor-core kernel; float32 always takes the FMA kernel."""
     from kairyu_b200.engine.workspace import Workspace
     from kairyu_b200.parts import FEED_FORWARDS, PartSpec, StepContext
 
