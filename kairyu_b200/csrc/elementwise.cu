@@ -3,11 +3,11 @@
 #include "common.cuh"
 
 // ------------------------------------------------------------------ embedding
-// out[t, :] = table[ids[t], :] as fp32 (the residual stream is fp32 in both
+// out[t, :] = table[ids[t], :] * scale as fp32 (the residual stream is fp32 in both
 // modes).  An id outside [0, V) writes zeros and raises KB_FLAG_BAD_TOKEN.
 template <typename TT>
 __global__ void embedding_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
-                                 float* __restrict__ out, int H, int V, int* flag) {
+                                 float* __restrict__ out, int H, int V, float scale, int* flag) {
     pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
@@ -18,18 +18,80 @@ __global__ void embedding_kernel(const TT* __restrict__ table, const int* __rest
         return;
     }
     const TT* src = table + (size_t)id * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = to_float(src[i]);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = to_float(src[i]) * scale;
 }
 
 KB_EXPORT int kb_embedding(const void* table, int table_is_bf16, const int* ids, float* out, int T,
-                           int H, int V, int* flag, cudaStream_t stream) {
+                           int H, int V, float scale, int* flag, cudaStream_t stream) {
     if (T == 0) return 0;
     if (!table || !ids || !out) return KB_ERR_NULL;
     const int threads = H >= 1024 ? 256 : 128;
     if (table_is_bf16)
-        kb_launch(embedding_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, (const __nv_bfloat16*)table, ids, out, H, V, flag);
+        kb_launch(embedding_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, (const __nv_bfloat16*)table, ids, out, H, V, scale, flag);
     else
-        kb_launch(embedding_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)table, ids, out, H, V, flag);
+        kb_launch(embedding_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)table, ids, out, H, V, scale, flag);
+    return kb_launch_result();
+}
+
+// ------------------------------------------------------------------ learned positions
+// x[t, :] += table[positions[t], :] on the fp32 residual.  A position outside [0, P) adds nothing
+// and raises KB_FLAG_BAD_POS.
+template <typename TT>
+__global__ void add_positions_kernel(const TT* __restrict__ table, const int* __restrict__ positions,
+                                     float* __restrict__ x, int H, int P, int* flag) {
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int p = positions[t];
+    if (p < 0 || p >= P) {
+        if (threadIdx.x == 0 && flag) atomicOr(flag, KB_FLAG_BAD_POS);
+        return;
+    }
+    const TT* src = table + (size_t)p * H;
+    float* dst = x + (size_t)t * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] += to_float(src[i]);
+}
+
+KB_EXPORT int kb_add_positions(const void* table, int table_is_bf16, const int* positions, float* x, int T, int H, int P,
+                               int* flag, cudaStream_t stream) {
+    if (T == 0) return 0;
+    if (!table || !positions || !x) return KB_ERR_NULL;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (table_is_bf16)
+        kb_launch(add_positions_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, (const __nv_bfloat16*)table, positions, x, H, P, flag);
+    else
+        kb_launch(add_positions_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)table, positions, x, H, P, flag);
+    return kb_launch_result();
+}
+
+// ------------------------------------------------------------------ activations of an ungated feed-forward
+// y = act(x), element by element, in 32-bit with one rounding at the store (in place is fine):
+//   0  relu(x)^2      1  gelu, tanh form: 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3)))      2  silu: x sigmoid(x)
+__device__ __forceinline__ float unary_activation(float x, int kind) {
+    if (kind == 0) {
+        const float r = fmaxf(x, 0.0f);
+        return r * r;
+    }
+    if (kind == 1) return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+    return x / (1.0f + expf(-x));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) activation_kernel(const T* __restrict__ x, T* __restrict__ y, size_t total, int kind) {
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+        y[i] = from_float<T>(unary_activation(to_float(x[i]), kind));
+}
+
+KB_EXPORT int kb_activation(const void* x, void* y, int is_bf16, long long total, int kind, cudaStream_t stream) {
+    if (total == 0) return 0;
+    if (!x || !y) return KB_ERR_NULL;
+    if (kind < 0 || kind > 2 || total < 0) return KB_ERR_BAD_ARG;
+    long long blocks = (total + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (is_bf16)
+        kb_launch(activation_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, stream, (const __nv_bfloat16*)x, (__nv_bfloat16*)y, (size_t)total, kind);
+    else
+        kb_launch(activation_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, stream, (const float*)x, (float*)y, (size_t)total, kind);
     return kb_launch_result();
 }
 

@@ -7,19 +7,24 @@
 //                 side by side (`sorted` lists the pairs run by run, `token_of` their tokens,
 //                 `place_of[p]` is where pair p stands, `ends[e]` where expert e's run ends), and
 //                 the runs are cut into tiles of MOE_TM pairs: tile -> (expert, first place, pairs).
-//   moe_activation  y = a * sigmoid(alpha a) * (b + 1) with a = min(gate, limit), b = clamp(up, +-limit)
+//   moe_route_scores  per token: softmax over all outputs, a correction that steers the choice only, groups of
+//                 neighbours of which the best stay, the K best that stay; weights = score * scale.  32-bit.
+//   moe_activation  y = a * sigmoid(alpha a) * (b + shift) with a = min(gate, limit), b = clamp(up, +-limit)
 //                 over rows [gate columns | up columns]: for the path whose products are a library's.
 //   moe_grouped   one block per (tile, 64 output columns): a [pairs, K] x [K, 64] product with the
 //                 tile's expert's weight.  Gated form: A rows are the tokens' activations (gathered
 //                 through the pair list), the weight holds the expert's gate rows and then its up
 //                 rows, and the epilogue is the expert's activation
-//                     a = min(gate, limit), b = clamp(up, -limit, limit), y = a * sigmoid(alpha a) * (b + 1)
+//                     a = min(gate, limit), b = clamp(up, -limit, limit), y = a * sigmoid(alpha a) * (b + shift)
+//                 (limit infinite, alpha 1, shift 0: silu(gate) * up)
 //                 written at the pair's place in `sorted`.  Plain form: A rows are those y rows, and
 //                 the result goes, in 32-bit, to row p of the output, so that the K rows of a token lie
 //                 together and whoever adds them (weighted by the router) does so in the order of k.
 //                 bfloat16 runs on mma.sync m16n8k16 with 32-bit accumulators, float32 on FMAs; the
 //                 sum over K runs in ascending order in both, whatever else the tile holds.
-//   moe_combine   out[t] = sum_k weight[t, k] * rows[at(t * K + k)]   (for callers that want plain rows)
+//   moe_combine   out[t] = sum_k weight[t, k] * rows[at(t * K + k)]   (for callers that want plain rows); a pair whose
+//                 id is not below the number of experts with weights is an identity expert: its row is the token's own.
+//                 The grouped kernels skip such pairs' tiles.
 #include "common.cuh"
 
 #define MOE_TM 64
@@ -77,10 +82,11 @@ moe_route_kernel(const float* __restrict__ logits, const TB* __restrict__ bias, 
     }
 }
 
-__device__ __forceinline__ float expert_activation(float gate, float up, float limit, float alpha) {
+// limit may be infinite (no clamps); alpha = 1, shift = 0 is the plain unit silu(gate) * up
+__device__ __forceinline__ float expert_activation(float gate, float up, float limit, float alpha, float shift) {
     const float a = fminf(gate, limit);
     const float b = fminf(fmaxf(up, -limit), limit);
-    return a * (1.0f / (1.0f + expf(-alpha * a))) * (b + 1.0f);
+    return a * (1.0f / (1.0f + expf(-alpha * a))) * (b + shift);
 }
 
 __global__ void __launch_bounds__(1024)
@@ -122,13 +128,13 @@ moe_plan_kernel(const int* __restrict__ ids, int pairs, int E, int top, int* __r
 
 template <typename T>
 __global__ void __launch_bounds__(256)
-moe_activation_kernel(const T* __restrict__ gate_up, T* __restrict__ y, int F, float limit, float alpha, size_t total) {
+moe_activation_kernel(const T* __restrict__ gate_up, T* __restrict__ y, int F, float limit, float alpha, float shift, size_t total) {
     pdl_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const size_t row = i / F, col = i % F;
     const float gate = to_float(gate_up[row * 2 * F + col]), up = to_float(gate_up[row * 2 * F + F + col]);
-    y[i] = from_float<T>(expert_activation(gate, up, limit, alpha));
+    y[i] = from_float<T>(expert_activation(gate, up, limit, alpha, shift));
 }
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
@@ -167,7 +173,7 @@ __global__ void __launch_bounds__(128)
 moe_grouped_kernel(const T* __restrict__ A, int lda, const int* __restrict__ sorted, int top, const T* __restrict__ W,
                    int N, int Kd, const int* __restrict__ tile_expert, const int* __restrict__ tile_first,
                    const int* __restrict__ tile_pairs, const int* __restrict__ num_tiles, float limit, float alpha,
-                   void* __restrict__ out, int vec) {
+                   float shift, int real_experts, void* __restrict__ out, int vec) {
     constexpr int LD = MoeTile<T>::LD;
     constexpr int CHUNK = MoeTile<T>::CHUNK;
     constexpr int NB = GATED ? 2 : 1;
@@ -179,6 +185,7 @@ moe_grouped_kernel(const T* __restrict__ A, int lda, const int* __restrict__ sor
     const int tile = blockIdx.x;
     if (tile >= *num_tiles) return;
     const int expert = tile_expert[tile], first = tile_first[tile], rows = tile_pairs[tile];
+    if (expert >= real_experts) return;  // a run of pairs whose "expert" has no weights (an identity expert): the sum takes the token's row itself
     const int n0 = blockIdx.y * MOE_TN;
     for (int i = threadIdx.x; i < MOE_TM; i += blockDim.x) {
         int src = -1, dst = -1;
@@ -259,7 +266,7 @@ moe_grouped_kernel(const T* __restrict__ A, int lda, const int* __restrict__ sor
                         if (n >= N) continue;
                         if constexpr (GATED)
                             reinterpret_cast<T*>(out)[(size_t)dst * N + n] =
-                                from_float<T>(expert_activation(acc[0][i][j][half * 2 + c], acc[1][i][j][half * 2 + c], limit, alpha));
+                                from_float<T>(expert_activation(acc[0][i][j][half * 2 + c], acc[1][i][j][half * 2 + c], limit, alpha, shift));
                         else
                             reinterpret_cast<float*>(out)[(size_t)dst * N + n] = acc[0][i][j][half * 2 + c];
                     }
@@ -311,7 +318,7 @@ moe_grouped_kernel(const T* __restrict__ A, int lda, const int* __restrict__ sor
                 const int n = n0 + tx + 8 * j;
                 if (n >= N) continue;
                 if constexpr (GATED)
-                    reinterpret_cast<T*>(out)[(size_t)dst * N + n] = from_float<T>(expert_activation(acc[0][i][j], acc[NB - 1][i][j], limit, alpha));
+                    reinterpret_cast<T*>(out)[(size_t)dst * N + n] = from_float<T>(expert_activation(acc[0][i][j], acc[NB - 1][i][j], limit, alpha, shift));
                 else
                     reinterpret_cast<float*>(out)[(size_t)dst * N + n] = acc[0][i][j];
             }
@@ -335,7 +342,7 @@ __global__ void __launch_bounds__(128)
 moe_skinny_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int* __restrict__ sorted, int top,
                   const __nv_bfloat16* __restrict__ W, int N, int Kd, int Kp, const int* __restrict__ tile_expert,
                   const int* __restrict__ tile_first, const int* __restrict__ tile_pairs, const int* __restrict__ num_tiles,
-                  float limit, float alpha, void* __restrict__ out) {
+                  float limit, float alpha, float shift, int real_experts, void* __restrict__ out) {
     extern __shared__ __align__(16) unsigned char sk_shared[];
     __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(sk_shared);  // [SK_PAIRS][Kp + 32]
     constexpr int NB = GATED ? 2 : 1;
@@ -344,6 +351,7 @@ moe_skinny_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int* __res
     const int tile = blockIdx.x;
     if (tile >= *num_tiles) return;
     const int expert = tile_expert[tile], first = tile_first[tile], rows = tile_pairs[tile];
+    if (expert >= real_experts) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, tg = lane & 3;
     const int f0 = blockIdx.y * SK_FEATURES + warp * 16;
@@ -423,7 +431,7 @@ moe_skinny_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int* __res
             const int place = first + sub + i;
             if constexpr (GATED)
                 reinterpret_cast<__nv_bfloat16*>(out)[(size_t)place * N + feature] =
-                    __float2bfloat16_rn(expert_activation(acc[0][c], acc[NB - 1][c], limit, alpha));
+                    __float2bfloat16_rn(expert_activation(acc[0][c], acc[NB - 1][c], limit, alpha, shift));
             else
                 reinterpret_cast<float*>(out)[(size_t)sorted[place] * N + feature] = acc[0][c];
         }
@@ -433,17 +441,120 @@ moe_skinny_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int* __res
 template <typename TR, typename TO>
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const TR* __restrict__ rows, const float* __restrict__ weights, const int* __restrict__ at, int K, int H,
-                   TO* __restrict__ out) {
+                   TO* __restrict__ out, const int* __restrict__ ids, const TO* __restrict__ x, int real_experts) {
     pdl_wait();
     const int t = blockIdx.x;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         float v = 0.0f;
         for (int k = 0; k < K; ++k) {
             const size_t p = (size_t)t * K + k;
-            v += weights[p] * to_float(rows[(at ? (size_t)at[p] : p) * H + i]);
+            if (ids && ids[p] >= real_experts)  // an identity expert: its output is the token's own row
+                v += weights[p] * to_float(x[(size_t)t * H + i]);
+            else
+                v += weights[p] * to_float(rows[(at ? (size_t)at[p] : p) * H + i]);
         }
         out[(size_t)t * H + i] = from_float<TO>(v);
     }
+}
+
+// Routing by scores: s = softmax(logits) over all n outputs; the choice runs on c = s + correction
+// (the correction steers the choice only).  The outputs form `groups` equal runs of neighbours; a
+// group's value is its largest c, the `keep` best groups stay (ties: the lower group) and the rest
+// count as minus infinity.  The K largest c that stay are chosen (ties: the lower index); their
+// weights are s * scale, not renormalised.  One warp a token; 32-bit.
+template <typename TB>
+__global__ void __launch_bounds__(128)
+moe_route_scores_kernel(const float* __restrict__ logits, const TB* __restrict__ correction, int n, int K, int groups, int keep,
+                        float scale, int* __restrict__ ids, float* __restrict__ weights, int T) {
+    extern __shared__ float route_shared[];  // per warp: s[n], c[n], group values [groups]
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (t >= T) return;
+    float* s = route_shared + (size_t)warp * (2 * n + groups);
+    float* c = s + n;
+    float* group_value = c + n;
+    const float* z = logits + (size_t)t * n;
+    float top = -INFINITY;
+    for (int e = lane; e < n; e += 32) top = fmaxf(top, z[e]);
+    top = warp_max(top);
+    float sum = 0.0f;
+    for (int e = lane; e < n; e += 32) {
+        const float p = expf(z[e] - top);
+        s[e] = p;
+        sum += p;
+    }
+    sum = warp_sum(sum);
+    for (int e = lane; e < n; e += 32) {
+        s[e] = s[e] / sum;
+        c[e] = s[e] + (correction ? to_float(correction[e]) : 0.0f);
+    }
+    __syncwarp();
+    const int per = n / groups;
+    if (keep < groups) {
+        for (int g = lane; g < groups; g += 32) {
+            float best = -INFINITY;
+            for (int e = g * per; e < (g + 1) * per; ++e) best = fmaxf(best, c[e]);
+            group_value[g] = best;
+        }
+        __syncwarp();
+        // group g stays if fewer than `keep` groups come before it in the order (value down, index up)
+        for (int g = lane; g < groups; g += 32) {
+            const float mine = group_value[g];
+            int before = 0;
+            for (int o = 0; o < groups; ++o) before += (group_value[o] > mine || (group_value[o] == mine && o < g)) ? 1 : 0;
+            if (before >= keep)
+                for (int e = g * per; e < (g + 1) * per; ++e) c[e] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    float last_value = INFINITY;
+    int last_id = -1;
+    for (int k = 0; k < K; ++k) {
+        float best = -INFINITY;
+        int best_id = 0x7fffffff;
+        for (int e = lane; e < n; e += 32) {
+            const float v = c[e];
+            const bool after = v < last_value || (v == last_value && e > last_id);
+            if (after && (v > best || (v == best && e < best_id))) {
+                best = v;
+                best_id = e;
+            }
+        }
+#pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1) {
+            const float other = __shfl_xor_sync(0xffffffffu, best, offset);
+            const int other_id = __shfl_xor_sync(0xffffffffu, best_id, offset);
+            if (other > best || (other == best && other_id < best_id)) {
+                best = other;
+                best_id = other_id;
+            }
+        }
+        if (best_id >= n) best_id = 0;  // fewer than K outputs stayed: nothing sensible is left to choose
+        if (lane == 0) {
+            ids[(size_t)t * K + k] = best_id;
+            weights[(size_t)t * K + k] = s[best_id] * scale;
+        }
+        last_value = best;
+        last_id = best_id;
+    }
+}
+
+KB_EXPORT int kb_moe_route_scores(const float* logits, const void* correction, int correction_is_bf16, int n, int K, int groups,
+                                  int keep, float scale, int* ids, float* weights, int T, cudaStream_t stream) {
+    if (T == 0) return 0;
+    if (!logits || !ids || !weights) return KB_ERR_NULL;
+    if (n < 1 || K < 1 || K > n || n > MOE_MAX_EXPERTS) return KB_ERR_UNSUPPORTED_SIZE;
+    if (groups < 1 || n % groups != 0 || keep < 1 || keep > groups || K > keep * (n / groups)) return KB_ERR_BAD_ARG;
+    const size_t smem = (size_t)4 * (2 * n + groups) * sizeof(float);
+    if (smem > 48 * 1024) return KB_ERR_UNSUPPORTED_SIZE;
+    if (correction_is_bf16)
+        kb_launch(moe_route_scores_kernel<__nv_bfloat16>, dim3((T + 3) / 4), dim3(128), smem, stream, logits, (const __nv_bfloat16*)correction,
+                  n, K, groups, keep, scale, ids, weights, T);
+    else
+        kb_launch(moe_route_scores_kernel<float>, dim3((T + 3) / 4), dim3(128), smem, stream, logits, (const float*)correction, n, K, groups,
+                  keep, scale, ids, weights, T);
+    return kb_launch_result();
 }
 
 KB_EXPORT int kb_moe_route(const float* logits, const void* bias, int bias_is_bf16, int E, int K, int* ids, float* weights, int T,
@@ -470,21 +581,23 @@ KB_EXPORT int kb_moe_plan(const int* ids, int pairs, int E, int top, int* sorted
     return kb_launch_result();
 }
 
-KB_EXPORT int kb_moe_activation(const void* gate_up, void* y, int is_bf16, int rows, int F, float limit, float alpha, cudaStream_t stream) {
+KB_EXPORT int kb_moe_activation(const void* gate_up, void* y, int is_bf16, int rows, int F, float limit, float alpha, float shift,
+                                cudaStream_t stream) {
     if (rows == 0) return 0;
     if (!gate_up || !y) return KB_ERR_NULL;
     const size_t total = (size_t)rows * F;
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (is_bf16)
-        kb_launch(moe_activation_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)y, F, limit, alpha, total);
+        kb_launch(moe_activation_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)y, F, limit, alpha, shift, total);
     else
-        kb_launch(moe_activation_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)gate_up, (float*)y, F, limit, alpha, total);
+        kb_launch(moe_activation_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)gate_up, (float*)y, F, limit, alpha, shift, total);
     return kb_launch_result();
 }
 
 KB_EXPORT int kb_moe_grouped(const void* A, int lda, const int* sorted, int top, const void* W, int N, int Kd, int is_bf16,
                              int gated, const int* tile_expert, const int* tile_first, const int* tile_pairs,
-                             const int* num_tiles, int max_tiles, float limit, float alpha, void* out, cudaStream_t stream) {
+                             const int* num_tiles, int max_tiles, float limit, float alpha, float shift, int real_experts, void* out,
+                             cudaStream_t stream) {
     if (max_tiles == 0) return 0;
     if (!A || !sorted || !W || !tile_expert || !tile_first || !tile_pairs || !num_tiles || !out) return KB_ERR_NULL;
     if (N < 1 || Kd < 1 || top < 1) return KB_ERR_BAD_ARG;
@@ -493,7 +606,7 @@ KB_EXPORT int kb_moe_grouped(const void* A, int lda, const int* sorted, int top,
     dim3 grid(max_tiles, (N + MOE_TN - 1) / MOE_TN);
 #define LAUNCH(T, G)                                                                                                          \
     kb_launch(moe_grouped_kernel<T, G>, grid, dim3(128), 0, stream, (const T*)A, lda, sorted, top, (const T*)W, N, Kd, tile_expert, \
-              tile_first, tile_pairs, num_tiles, limit, alpha, out, vec)
+              tile_first, tile_pairs, num_tiles, limit, alpha, shift, real_experts, out, vec)
     if (is_bf16) {
         if (gated) LAUNCH(__nv_bfloat16, true); else LAUNCH(__nv_bfloat16, false);
     } else {
@@ -505,7 +618,7 @@ KB_EXPORT int kb_moe_grouped(const void* A, int lda, const int* sorted, int top,
 
 KB_EXPORT int kb_moe_skinny(const void* A, int lda, const int* sorted, int top, const void* W, int N, int Kd, int gated,
                             const int* tile_expert, const int* tile_first, const int* tile_pairs, const int* num_tiles,
-                            int max_tiles, float limit, float alpha, void* out, cudaStream_t stream) {
+                            int max_tiles, float limit, float alpha, float shift, int real_experts, void* out, cudaStream_t stream) {
     if (max_tiles == 0) return 0;
     if (!A || !sorted || !W || !tile_expert || !tile_first || !tile_pairs || !num_tiles || !out) return KB_ERR_NULL;
     if (N < 1 || Kd < 8 || top < 1 || Kd % 8 != 0 || lda % 8 != 0 || ((uintptr_t)A % 16) != 0 || ((uintptr_t)W % 16) != 0) return KB_ERR_BAD_ARG;
@@ -516,20 +629,22 @@ KB_EXPORT int kb_moe_skinny(const void* A, int lda, const int* sorted, int top, 
     if (gated) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(moe_skinny_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         kb_launch(moe_skinny_kernel<true>, grid, dim3(128), smem, stream, (const __nv_bfloat16*)A, lda, sorted, top, (const __nv_bfloat16*)W, N, Kd, Kp,
-                  tile_expert, tile_first, tile_pairs, num_tiles, limit, alpha, out);
+                  tile_expert, tile_first, tile_pairs, num_tiles, limit, alpha, shift, real_experts, out);
     } else {
         if (smem > 48 * 1024) cudaFuncSetAttribute(moe_skinny_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         kb_launch(moe_skinny_kernel<false>, grid, dim3(128), smem, stream, (const __nv_bfloat16*)A, lda, sorted, top, (const __nv_bfloat16*)W, N, Kd, Kp,
-                  tile_expert, tile_first, tile_pairs, num_tiles, limit, alpha, out);
+                  tile_expert, tile_first, tile_pairs, num_tiles, limit, alpha, shift, real_experts, out);
     }
     return kb_launch_result();
 }
 
 KB_EXPORT int kb_moe_combine(const void* rows, int rows_is_bf16, const float* weights, const int* at, int K, int H, void* out,
-                             int out_is_bf16, int T, cudaStream_t stream) {
+                             int out_is_bf16, int T, const int* ids, const void* x, int real_experts, cudaStream_t stream) {
     if (T == 0) return 0;
-    if (!rows || !weights || !out) return KB_ERR_NULL;
-#define LAUNCH(TR, TO) kb_launch(moe_combine_kernel<TR, TO>, dim3(T), dim3(256), 0, stream, (const TR*)rows, weights, at, K, H, (TO*)out)
+    if (!rows || !weights || !out || (ids && !x)) return KB_ERR_NULL;
+#define LAUNCH(TR, TO)                                                                                                     \
+    kb_launch(moe_combine_kernel<TR, TO>, dim3(T), dim3(256), 0, stream, (const TR*)rows, weights, at, K, H, (TO*)out, ids, \
+              (const TO*)x, real_experts)
     if (rows_is_bf16) {
         if (out_is_bf16) LAUNCH(__nv_bfloat16, __nv_bfloat16); else LAUNCH(__nv_bfloat16, float);
     } else {

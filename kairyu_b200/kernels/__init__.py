@@ -109,8 +109,8 @@ def _fn(library: str, name: str, argtypes: list) -> ctypes._CFuncPtr:
 # ----------------------------------------------------------------------------- elementwise
 
 
-def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, flag: Optional[torch.Tensor] = None) -> None:
-    """out[t] = table[ids[t]] as fp32."""
+def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, flag: Optional[torch.Tensor] = None, *, scale: float = 1.0) -> None:
+    """out[t] = table[ids[t]] * scale as fp32."""
     _need_cuda("embedding", table, ids, out, flag)
     _need_i32("embedding", ids)
     V, H = table.shape
@@ -118,8 +118,33 @@ def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, flag: O
         raise KernelError("embedding: out must be contiguous fp32 [tokens, hidden]")
     if not table.is_contiguous():
         raise KernelError("embedding: table must be contiguous")
-    fn = _fn("elementwise", "kb_embedding", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
-    _check(fn(table.data_ptr(), _is_bf16(table, "embedding"), ids.data_ptr(), out.data_ptr(), ids.numel(), H, V, _ptr(flag), _stream()), "embedding")
+    fn = _fn("elementwise", "kb_embedding", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p])
+    _check(fn(table.data_ptr(), _is_bf16(table, "embedding"), ids.data_ptr(), out.data_ptr(), ids.numel(), H, V, float(scale), _ptr(flag), _stream()), "embedding")
+
+
+def add_positions(table: torch.Tensor, positions: torch.Tensor, x: torch.Tensor, flag: Optional[torch.Tensor] = None) -> None:
+    """x[t] += table[positions[t]] on the fp32 residual (learned absolute positions)."""
+    _need_cuda("add_positions", table, positions, x, flag)
+    _need_i32("add_positions", positions)
+    P, H = table.shape
+    if x.dtype != torch.float32 or x.shape != (positions.numel(), H) or not x.is_contiguous() or not table.is_contiguous():
+        raise KernelError("add_positions: x must be contiguous fp32 [tokens, hidden] and the table contiguous [positions, hidden]")
+    fn = _fn("elementwise", "kb_add_positions", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(fn(table.data_ptr(), _is_bf16(table, "add_positions"), positions.data_ptr(), x.data_ptr(), positions.numel(), H, P, _ptr(flag), _stream()), "add_positions")
+
+
+ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2}
+
+
+def activation(x: torch.Tensor, out: torch.Tensor, kind: str) -> None:
+    """out = act(x) element by element (``out`` may be ``x``): ``relu2`` = relu(x)^2, ``gelu_tanh``, ``silu``."""
+    _need_cuda("activation", x, out)
+    if kind not in ACTIVATIONS:
+        raise KernelError(f"activation: unknown kind {kind!r} ({', '.join(ACTIVATIONS)})")
+    if x.shape != out.shape or x.dtype != out.dtype or not (x.is_contiguous() and out.is_contiguous()):
+        raise KernelError("activation: contiguous tensors of one shape and dtype")
+    fn = _fn("elementwise", "kb_activation", [c_void_p, c_void_p, c_int, ctypes.c_longlong, c_int, c_void_p])
+    _check(fn(x.data_ptr(), out.data_ptr(), _is_bf16(x, "activation"), x.numel(), ACTIVATIONS[kind], _stream()), "activation")
 
 
 def patch_tokens(ids: torch.Tensor, source: torch.Tensor, sampled: torch.Tensor, flag: Optional[torch.Tensor] = None) -> None:
@@ -306,6 +331,102 @@ def paged_attention_generic(
         ),
         "paged_attention_generic",
     )
+
+
+def paged_kv_write(
+    packed: torch.Tensor,
+    k_offset: int,
+    v_offset: int,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    *,
+    positions: torch.Tensor,
+    row_ids: torch.Tensor,
+    block_table: torch.Tensor,
+    write_from: Optional[torch.Tensor] = None,
+    flag: Optional[torch.Tensor] = None,
+) -> None:
+    """Columns of a step's packed rows into the pages: a key row (all key/value heads side by side)
+    from ``k_offset`` on, a value row from ``v_offset`` on; the two may differ in width."""
+    _need_cuda("paged_kv_write", packed, k_cache, v_cache, positions, row_ids, block_table, write_from, flag)
+    _need_i32("paged_kv_write", positions, row_ids, block_table, write_from)
+    num_pages, page_size = k_cache.shape[:2]
+    k_width = k_cache.shape[2] * k_cache.shape[3]
+    v_width = v_cache.shape[2] * v_cache.shape[3]
+    if packed.dtype != k_cache.dtype or v_cache.dtype != k_cache.dtype or packed.stride(1) != 1 or v_cache.shape[:2] != k_cache.shape[:2]:
+        raise KernelError("paged_kv_write: one dtype, unit inner stride, caches of one page geometry")
+    if not k_cache.is_contiguous() or not v_cache.is_contiguous():
+        raise KernelError("paged_kv_write: caches must be contiguous")
+    if min(k_offset, v_offset) < 0 or k_offset + k_width > packed.shape[1] or v_offset + v_width > packed.shape[1]:
+        raise KernelError("paged_kv_write: the key or value columns lie outside the packed rows")
+    fn = _fn("diff_attention", "kb_paged_kv_write", [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                                     c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p])
+    _check(fn(packed.data_ptr(), packed.stride(0), _is_bf16(packed, "paged_kv_write"), packed.shape[0], int(k_offset), k_width, int(v_offset),
+              v_width, k_cache.data_ptr(), v_cache.data_ptr(), positions.data_ptr(), row_ids.data_ptr(), block_table.data_ptr(),
+              block_table.shape[1], _ptr(write_from), page_size, num_pages, _ptr(flag), _stream()), "paged_kv_write")
+
+
+def _check_diff_attention(what: str, q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, num_q_heads: int,
+                          maps: int) -> tuple[int, int, int, int, int]:
+    num_pages, page_size, num_kv_heads, key_width = k_cache.shape
+    if maps not in (1, 2) or key_width % maps:
+        raise KernelError(f"{what}: {maps} maps over key rows of {key_width}")
+    dim, vdim = key_width // maps, v_cache.shape[3]
+    if v_cache.shape[:3] != k_cache.shape[:3] or not k_cache.is_contiguous() or not v_cache.is_contiguous():
+        raise KernelError(f"{what}: caches must be contiguous and of one page geometry")
+    if q.dtype != k_cache.dtype or out.dtype != q.dtype or v_cache.dtype != q.dtype or q.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError(f"{what}: one dtype and unit inner strides")
+    if num_q_heads % num_kv_heads or q.shape[1] < num_q_heads * key_width or out.shape[1] < num_q_heads * vdim:
+        raise KernelError(f"{what}: heads or widths do not fit")
+    return num_pages, page_size, num_kv_heads, dim, vdim
+
+
+def diff_attention_generic(
+    q: torch.Tensor,
+    out: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    *,
+    positions: torch.Tensor,
+    row_ids: torch.Tensor,
+    block_table: torch.Tensor,
+    num_q_heads: int,
+    maps: int,
+    scale: float,
+    softcap: float = 0.0,
+    window: int = 0,
+    lam: float = 0.0,
+    head_norm_eps: Optional[float] = None,
+    out_scale: float = 1.0,
+    flag: Optional[torch.Tensor] = None,
+) -> None:
+    """Attention with ``maps`` softmax maps a head over the same values, every token of the step, in 32-bit
+    arithmetic.  ``q``: [tokens, >= heads * maps * dim], a head's maps side by side; the key cache
+    [pages, page, kv_heads, maps * dim] the same way; values [pages, page, kv_heads, vdim].  Scores
+    q.k * scale, capped as softcap * tanh(s / softcap) when softcap > 0; a token sees itself and the
+    ``window - 1`` before it (0: all).  o = a_1 - lam * a_2; with ``head_norm_eps`` each head's o is divided
+    by its root mean square (eps inside the root) and multiplied by ``out_scale``.  ``out``: [tokens, heads * vdim]."""
+    what = "diff_attention_generic"
+    _need_cuda(what, q, out, k_cache, v_cache, positions, row_ids, block_table, flag)
+    _need_i32(what, positions, row_ids, block_table)
+    num_pages, page_size, num_kv_heads, dim, vdim = _check_diff_attention(what, q, out, k_cache, v_cache, num_q_heads, maps)
+    if dim > 256 or vdim > 256:
+        raise KernelError(f"{what}: key width {dim} or value width {vdim} > 256 is not supported")
+    fn = _fn("diff_attention", "kb_diff_attention_generic",
+             [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+              c_int, c_int, c_int, c_float, c_float, c_int, c_float, c_int, c_float, c_float, c_void_p, c_void_p])
+    _check(fn(q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), _is_bf16(q, what),
+              positions.data_ptr(), row_ids.data_ptr(), block_table.data_ptr(), block_table.shape[1], q.shape[0], num_q_heads, num_kv_heads,
+              int(maps), dim, vdim, page_size, num_pages, float(scale), float(softcap), int(window), float(lam),
+              0 if head_norm_eps is None else 1, float(head_norm_eps or 0.0), float(out_scale), _ptr(flag), _stream()), what)
+
+
+DIFF_ATTENTION_TILE = 64  # queries a tile of the tensor-core kernel for prompt portions
+
+
+def diff_attention_mma_supported(head_dim: int, value_dim: int, num_q_heads: int, num_kv_heads: int) -> bool:
+    """Sizes the tensor-core kernels of differential attention take; others use the 32-bit-arithmetic kernel."""
+    return False
 
 
 DECODE_SPLIT = 128  # keys per split of the split-KV kernel (csrc/attention_mma.cu: DEC_SPLIT)
@@ -1364,6 +1485,24 @@ def moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], top: int, ids:
               weights.data_ptr(), T, _stream()), "moe_route")
 
 
+def moe_route_scores(logits: torch.Tensor, correction: Optional[torch.Tensor], top: int, ids: torch.Tensor, weights: torch.Tensor, *,
+                     groups: int = 1, keep: int = 1, scale: float = 1.0) -> None:
+    """Routing by scores (fp32): s = softmax(logits) over all outputs; the choice runs on s + correction within the
+    ``keep`` best of ``groups`` equal groups of neighbours (a group's value: its largest s + correction); the ``top``
+    best are chosen (ties: the lower index) and weigh s * scale, not renormalised."""
+    _need_cuda("moe_route_scores", logits, correction, ids, weights)
+    T, n = logits.shape
+    if logits.dtype != torch.float32 or not logits.is_contiguous() or weights.dtype != torch.float32 or ids.dtype != torch.int32:
+        raise KernelError("moe_route_scores: fp32 logits and weights, int32 ids")
+    if ids.shape != (T, top) or weights.shape != (T, top) or not ids.is_contiguous() or not weights.is_contiguous():
+        raise KernelError("moe_route_scores: ids and weights must be contiguous [tokens, top]")
+    if correction is not None and (correction.numel() != n or not correction.is_contiguous()):
+        raise KernelError("moe_route_scores: the correction must have one entry a router output")
+    fn = _fn("moe", "kb_moe_route_scores", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_void_p])
+    _check(fn(logits.data_ptr(), _ptr(correction), _is_bf16(correction, "moe_route_scores") if correction is not None else 0, n, int(top),
+              int(groups), int(keep), float(scale), ids.data_ptr(), weights.data_ptr(), T, _stream()), "moe_route_scores")
+
+
 def moe_plan(ids: torch.Tensor, experts: int, plan: torch.Tensor) -> dict:
     """Sort a step's (token, expert) pairs by expert and cut the runs into tiles.  ``ids`` [tokens, top];
     ``plan``: int32 scratch of at least ``moe_plan_size(pairs, experts)`` entries; returns views into it:
@@ -1408,19 +1547,19 @@ def moe_library_product(a: torch.Tensor, weight: torch.Tensor, ends: torch.Tenso
     return torch._grouped_mm(a, weight.transpose(1, 2), offs=ends)
 
 
-def moe_activation(gate_up: torch.Tensor, out: torch.Tensor, *, limit: float, alpha: float = 1.702) -> None:
-    """out = a * sigmoid(alpha a) * (b + 1), a = min(gate, limit), b = clamp(up, -limit, limit); ``gate_up`` rows hold
-    the gate columns and then the up columns."""
+def moe_activation(gate_up: torch.Tensor, out: torch.Tensor, *, limit: float, alpha: float = 1.702, shift: float = 1.0) -> None:
+    """out = a * sigmoid(alpha a) * (b + shift), a = min(gate, limit), b = clamp(up, -limit, limit); ``gate_up`` rows hold
+    the gate columns and then the up columns.  An infinite limit, alpha 1 and shift 0 give silu(gate) * up."""
     _need_cuda("moe_activation", gate_up, out)
     rows, wide = gate_up.shape
     if wide % 2 or out.shape != (rows, wide // 2) or out.dtype != gate_up.dtype or not (gate_up.is_contiguous() and out.is_contiguous()):
         raise KernelError("moe_activation: shape or dtype mismatch")
-    fn = _fn("moe", "kb_moe_activation", [c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p])
-    _check(fn(gate_up.data_ptr(), out.data_ptr(), _is_bf16(out, "moe_activation"), rows, wide // 2, float(limit), float(alpha), _stream()), "moe_activation")
+    fn = _fn("moe", "kb_moe_activation", [c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_float, c_void_p])
+    _check(fn(gate_up.data_ptr(), out.data_ptr(), _is_bf16(out, "moe_activation"), rows, wide // 2, float(limit), float(alpha), float(shift), _stream()), "moe_activation")
 
 
 def moe_grouped(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, plan: dict, *, top: int, gated: bool, limit: float = 0.0,
-                alpha: float = 1.702) -> None:
+                alpha: float = 1.702, shift: float = 1.0) -> None:
     """The experts' products over a planned step.  ``gated``: ``a`` [tokens, K] activations, ``weight``
     [experts, 2 * N, K] (gate rows, then up rows), ``out`` [pairs, N] in the activations' dtype, rows
     in the plan's sorted order, after the experts' activation.  Otherwise ``a`` is such an ``out``,
@@ -1434,10 +1573,10 @@ def moe_grouped(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, plan: 
     if out.shape != (pairs, N) or out.dtype != (a.dtype if gated else torch.float32):
         raise KernelError("moe_grouped: the output does not fit")
     fn = _fn("moe", "kb_moe_grouped", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
-                                        c_void_p, c_int, c_float, c_float, c_void_p, c_void_p])
+                                        c_void_p, c_int, c_float, c_float, c_float, c_int, c_void_p, c_void_p])
     _check(fn(a.data_ptr(), a.stride(0), plan["sorted"].data_ptr(), int(top), weight.data_ptr(), N, K, _is_bf16(a, "moe_grouped"), 1 if gated else 0,
               plan["tile_expert"].data_ptr(), plan["tile_first"].data_ptr(), plan["tile_pairs"].data_ptr(), plan["num_tiles"].data_ptr(),
-              plan["max_tiles"], float(limit), float(alpha), out.data_ptr(), _stream()), "moe_grouped")
+              plan["max_tiles"], float(limit), float(alpha), float(shift), experts, out.data_ptr(), _stream()), "moe_grouped")
 
 
 # The few-pairs kernel is taken for up to this many tokens a step, in models this narrow: measured against the
@@ -1457,7 +1596,7 @@ def moe_skinny_ok(tokens: int, hidden: int, intermediate: int, dtype: torch.dtyp
 
 
 def moe_skinny(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, plan: dict, *, top: int, gated: bool, limit: float = 0.0,
-               alpha: float = 1.702) -> None:
+               alpha: float = 1.702, shift: float = 1.0) -> None:
     """``moe_grouped`` for few pairs an expert (bfloat16): the weight rows are the tensor cores' M side, up to 8
     pairs at a time the N side, and the weights are read straight from global memory.  Same operands and results."""
     _need_cuda("moe_skinny", a, weight, out)
@@ -1469,19 +1608,25 @@ def moe_skinny(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, plan: d
     if out.shape != (pairs, N) or out.dtype != (torch.bfloat16 if gated else torch.float32):
         raise KernelError("moe_skinny: the output does not fit")
     fn = _fn("moe", "kb_moe_skinny", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
-                                       c_void_p, c_int, c_float, c_float, c_void_p, c_void_p])
+                                       c_void_p, c_int, c_float, c_float, c_float, c_int, c_void_p, c_void_p])
     _check(fn(a.data_ptr(), a.stride(0), plan["sorted"].data_ptr(), int(top), weight.data_ptr(), N, K, 1 if gated else 0,
               plan["tile_expert"].data_ptr(), plan["tile_first"].data_ptr(), plan["tile_pairs"].data_ptr(), plan["num_tiles"].data_ptr(),
-              plan["max_tiles"], float(limit), float(alpha), out.data_ptr(), _stream()), "moe_skinny")
+              plan["max_tiles"], float(limit), float(alpha), float(shift), experts, out.data_ptr(), _stream()), "moe_skinny")
 
 
-def moe_combine(rows: torch.Tensor, weights: torch.Tensor, out: torch.Tensor, at: Optional[torch.Tensor] = None) -> None:
-    """out[t] = sum_k weights[t, k] * rows[t * K + k] (or rows[at[t * K + k]]): fp32 sum, in the order of k."""
-    _need_cuda("moe_combine", rows, weights, out, at)
-    _need_i32("moe_combine", at)
+def moe_combine(rows: torch.Tensor, weights: torch.Tensor, out: torch.Tensor, at: Optional[torch.Tensor] = None, *,
+                ids: Optional[torch.Tensor] = None, x: Optional[torch.Tensor] = None, experts: int = 0) -> None:
+    """out[t] = sum_k weights[t, k] * rows[t * K + k] (or rows[at[t * K + k]]): fp32 sum, in the order of k.  With ``ids``
+    [tokens, K], ``x`` [tokens, H] (out's dtype) and ``experts``: a pair whose id is ``experts`` or more is an identity
+    expert and contributes the token's own row ``x[t]``."""
+    _need_cuda("moe_combine", rows, weights, out, at, ids, x)
+    _need_i32("moe_combine", at, ids)
+    if ids is not None and (x is None or x.dtype != out.dtype or x.shape != out.shape or not x.is_contiguous() or ids.shape != weights.shape):
+        raise KernelError("moe_combine: identity experts need the tokens' rows in the output's dtype and shape, and ids [tokens, K]")
     T, K = weights.shape
     H = rows.shape[1]
     if weights.dtype != torch.float32 or rows.shape[0] != T * K or out.shape != (T, H) or not (rows.is_contiguous() and weights.is_contiguous() and out.is_contiguous()):
         raise KernelError("moe_combine: shape or dtype mismatch")
-    fn = _fn("moe", "kb_moe_combine", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p])
-    _check(fn(rows.data_ptr(), _is_bf16(rows, "moe_combine"), weights.data_ptr(), _ptr(at), K, H, out.data_ptr(), _is_bf16(out, "moe_combine"), T, _stream()), "moe_combine")
+    fn = _fn("moe", "kb_moe_combine", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p])
+    _check(fn(rows.data_ptr(), _is_bf16(rows, "moe_combine"), weights.data_ptr(), _ptr(at), K, H, out.data_ptr(), _is_bf16(out, "moe_combine"), T,
+              _ptr(ids), _ptr(x), int(experts), _stream()), "moe_combine")

@@ -31,6 +31,7 @@ LIBRARIES: dict[str, list[str]] = {
     "elementwise": [],
     "rope_kv": [],
     "attention_generic": [],
+    "diff_attention": [],
     "attention_mma": [],
     "attention_decode_static": [],
     "attention_decode_tma": [],

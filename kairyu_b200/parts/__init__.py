@@ -1,7 +1,9 @@
 """Model parts and their registries.  Importing this package registers the
 built-in parts; more can be registered from outside with the same decorators."""
 
-from kairyu_b200.parts import attention, block, delta_rule, embedding, ffn, latent_attention, moe, norm, rope  # noqa: F401  (registration)
+from kairyu_b200.parts import (  # noqa: F401  (registration)
+    attention, block, delta_rule, diff_attention, embedding, ffn, latent_attention, learned_positions, moe, norm, rope,
+)
 from kairyu_b200.parts.base import (
     BLOCKS,
     EMBEDDINGS,

@@ -43,9 +43,10 @@ class PreNormBlock(Block):
         context = dict(dtype=dtype, device=device, shared=shared)
         self.mixer_norm = NORMS.build(layer.mixer_norm, **context)
         self.mixer = MIXERS.build(layer.mixer, **context)
-        self.ffn_norm = NORMS.build(layer.ffn_norm, **context)
-        self.ffn = FEED_FORWARDS.build(layer.ffn, **context)
-        self._parts = (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn)
+        # a layer may have no feed-forward: the block is then x += mixer(norm(x)) alone
+        self.ffn_norm = NORMS.build(layer.ffn_norm, **context) if layer.ffn is not None else None
+        self.ffn = FEED_FORWARDS.build(layer.ffn, **context) if layer.ffn is not None else None
+        self._parts = tuple(part for part in (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn) if part is not None)
 
     def tensor_specs(self) -> list[TensorSpec]:
         return [spec for part in self._parts for spec in part.tensor_specs()]
@@ -58,7 +59,7 @@ class PreNormBlock(Block):
         return sum(part.bytes_streamed() for part in self._parts)
 
     def _fused(self, ctx: StepContext) -> bool:
-        if ctx.dtype != torch.bfloat16 or not kernels.fused_norm_available():
+        if ctx.dtype != torch.bfloat16 or self.ffn is None or not kernels.fused_norm_available():
             return False
         if not (hasattr(self.mixer_norm, "fold_target") and hasattr(self.ffn_norm, "fold_target")):
             return False  # a norm offers ``fold_target`` when the products around it can take its two halves
@@ -82,6 +83,8 @@ class PreNormBlock(Block):
             normed = delta
         else:
             normed = self.mixer_norm.apply(residual, delta, ctx)
+        if self.ffn is None:
+            return residual, self.mixer.forward(normed, ctx, cache)
         if not self._fused(ctx):
             mixed = self.mixer.forward(normed, ctx, cache)
             normed = self.ffn_norm.apply(residual, mixed, ctx)

@@ -12,12 +12,13 @@ from kairyu_b200.parts.base import EMBEDDINGS, HEADS, Part, StepContext, TensorS
 
 @EMBEDDINGS.register("token_embedding")
 class TokenEmbedding(Part):
-    """``x = E[token_ids]``, no scaling; the residual it starts is fp32."""
+    """``x = E[token_ids] * scale`` (``scale`` 1 unless given); the residual it starts is fp32."""
 
     graph_safe = True
 
-    def __init__(self, *, name: str, vocab_size: int, hidden_size: int, dtype: torch.dtype, device: str, **_: object) -> None:
+    def __init__(self, *, name: str, vocab_size: int, hidden_size: int, dtype: torch.dtype, device: str, scale: float = 1.0, **_: object) -> None:
         self.name = name
+        self.scale = float(scale)
         self.vocab_size = vocab_size
         self.hidden_size = hidden_size
         self.weight: Optional[torch.Tensor] = None
@@ -30,7 +31,7 @@ class TokenEmbedding(Part):
 
     def forward(self, ctx: StepContext) -> torch.Tensor:
         out = ctx.workspace.buffer("residual", ctx.num_tokens, self.hidden_size, torch.float32)
-        kernels.embedding(self.weight, ctx.token_ids, out, ctx.error_flag)
+        kernels.embedding(self.weight, ctx.token_ids, out, ctx.error_flag, scale=self.scale)
         return out
 
 

@@ -71,3 +71,60 @@ class SwiGLU(FeedForward):
         out = ws.buffer("ffn.out", tokens, self.hidden_size, self.dtype)
         kernels.linear(hidden, self.w_down, None, out)
         return out
+
+
+@FEED_FORWARDS.register("mlp")
+class UngatedMLP(FeedForward):
+    """``down(act(up(x)))`` without a gate and without biases.  ``activation``: ``relu2`` (the square of
+    relu), ``gelu_tanh`` or ``silu``; it runs in 32-bit on the up product's rows, with one rounding at
+    the store.  ``up_name`` / ``down_name``: the two tensors' names under ``prefix``."""
+
+    graph_safe = True
+
+    def __init__(
+        self,
+        *,
+        prefix: str,
+        hidden_size: int,
+        intermediate_size: int,
+        activation: str,
+        up_name: str = "up",
+        down_name: str = "down",
+        dtype: torch.dtype,
+        device: str,
+        **_: object,
+    ) -> None:
+        if activation not in kernels.ACTIVATIONS:
+            raise ValueError(f"feed-forward activation {activation!r} is not implemented ({', '.join(kernels.ACTIVATIONS)})")
+        self.prefix = prefix
+        self.hidden_size = hidden_size
+        self.intermediate_size = intermediate_size
+        self.activation = activation
+        self.up_name = f"{prefix}.{up_name}"
+        self.down_name = f"{prefix}.{down_name}"
+        self.dtype = dtype
+        self.w_up: Optional[torch.Tensor] = None
+        self.w_down: Optional[torch.Tensor] = None
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        return [
+            TensorSpec(self.up_name, (self.intermediate_size, self.hidden_size)),
+            TensorSpec(self.down_name, (self.hidden_size, self.intermediate_size)),
+        ]
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        self.w_up = tensors[self.up_name].contiguous()
+        self.w_down = tensors[self.down_name].contiguous()
+
+    def bytes_streamed(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.w_up, self.w_down))
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        tokens = x.shape[0]
+        ws = ctx.workspace
+        hidden = ws.buffer("mlp.hidden", tokens, self.intermediate_size, self.dtype)
+        kernels.linear(x, self.w_up, None, hidden)
+        kernels.activation(hidden, hidden, self.activation)
+        out = ws.buffer("mlp.out", tokens, self.hidden_size, self.dtype)
+        kernels.linear(hidden, self.w_down, None, out)
+        return out

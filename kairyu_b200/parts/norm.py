@@ -12,23 +12,28 @@ from kairyu_b200.parts.base import NORMS, Norm, StepContext, TensorSpec
 
 @NORMS.register("rmsnorm")
 class RMSNorm(Norm):
-    """``y = x * rsqrt(mean(x^2) + eps) * weight`` with fp32 statistics."""
+    """``y = x * rsqrt(mean(x^2) + eps) * (offset + weight)`` with fp32 statistics.  ``offset`` is 0 unless
+    given; a file that stores its norm weights around zero names 1, and the sum is then formed once,
+    at loading, in 32-bit, and held so."""
 
     graph_safe = True
 
-    def __init__(self, *, name: str, size: int, eps: float, dtype: torch.dtype, device: str, **_: object) -> None:
+    def __init__(self, *, name: str, size: int, eps: float, dtype: torch.dtype, device: str, offset: float = 0.0, **_: object) -> None:
         self.name = name  # full tensor name of the weight
         self.size = size
         self.eps = float(eps)
+        self.offset = float(offset)
         self.dtype = dtype
         self.device = device
         self.weight: Optional[torch.Tensor] = None
 
     def tensor_specs(self) -> list[TensorSpec]:
-        return [TensorSpec(self.name, (self.size,), role="vector", init="norm")]
+        return [TensorSpec(self.name, (self.size,), role="vector", init="norm" if self.offset == 0.0 else "normal")]
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         self.weight = tensors[self.name].contiguous()
+        if self.offset != 0.0:
+            self.weight = (self.weight.float() + self.offset).contiguous()
 
     def bytes_streamed(self) -> int:
         return self.weight.numel() * self.weight.element_size()

@@ -62,6 +62,9 @@ def _register_builtin() -> None:
     from kairyu_b200.models import makilorn
 
     register_architecture("Makilorn", makilorn.parse_makilorn, makilorn.makilorn_spec)
+    from kairyu_b200.models import karesun
+
+    register_architecture("Karesun", karesun.parse_karesun, karesun.karesun_spec)
 
 
 _register_builtin()
