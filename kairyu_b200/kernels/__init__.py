@@ -425,8 +425,54 @@ DIFF_ATTENTION_TILE = 64  # queries a tile of the tensor-core kernel for prompt 
 
 
 def diff_attention_mma_supported(head_dim: int, value_dim: int, num_q_heads: int, num_kv_heads: int) -> bool:
-    """Sizes the tensor-core kernels of differential attention take; others use the 32-bit-arithmetic kernel."""
-    return False
+    """Sizes the tensor-core kernel of differential attention takes (bfloat16; key and value widths multiples of 16
+    up to 128, up to 64 query heads a key/value head); others use the 32-bit-arithmetic kernel."""
+    return (head_dim % 16 == 0 and 16 <= head_dim <= 128 and value_dim % 16 == 0 and 16 <= value_dim <= 128
+            and num_kv_heads >= 1 and num_q_heads % num_kv_heads == 0 and num_q_heads // num_kv_heads <= 64)
+
+
+def diff_attention_mma(
+    q: torch.Tensor,
+    out: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    *,
+    ctx: object,
+    block_table: torch.Tensor,
+    num_q_heads: int,
+    maps: int,
+    scale: float,
+    softcap: float = 0.0,
+    window: int = 0,
+    lam: float = 0.0,
+    head_norm_eps: Optional[float] = None,
+    out_scale: float = 1.0,
+    flag: Optional[torch.Tensor] = None,
+) -> None:
+    """``diff_attention_generic`` on tensor cores (bfloat16, two maps): the step's prompt portions go tile by
+    tile (``ctx.tiles[DIFF_ATTENTION_TILE]``), its single-token rows a key/value head at a time
+    (``ctx.decode_rows``), in two launches of one kernel.  ``ctx``: the step's description."""
+    what = "diff_attention_mma"
+    _need_cuda(what, q, out, k_cache, v_cache, block_table, flag)
+    _need_i32(what, block_table)
+    num_pages, page_size, num_kv_heads, dim, vdim = _check_diff_attention(what, q, out, k_cache, v_cache, num_q_heads, maps)
+    if maps != 2 or q.dtype != torch.bfloat16 or not diff_attention_mma_supported(dim, vdim, num_q_heads, num_kv_heads):
+        raise KernelError(f"{what}: bfloat16, two maps, sizes as diff_attention_mma_supported says")
+    fn = _fn("diff_attention_mma", "kb_diff_attention_mma",
+             [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+              c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_float, c_int, c_float, c_float, c_void_p, c_void_p])
+
+    def launch(rows: torch.Tensor, second: torch.Tensor, count: int, single: int) -> None:
+        _check(fn(q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), ctx.qo_indptr.data_ptr(),
+                  ctx.seq_lens.data_ptr(), block_table.data_ptr(), block_table.shape[1], rows.data_ptr(), second.data_ptr(), int(count), single,
+                  num_q_heads, num_kv_heads, dim, vdim, page_size, num_pages, float(scale), float(softcap), int(window), float(lam),
+                  0 if head_norm_eps is None else 1, float(head_norm_eps or 0.0), float(out_scale), _ptr(flag), _stream()), what)
+
+    num_tiles, tile_rows, tile_starts = ctx.tiles[DIFF_ATTENTION_TILE]
+    if num_tiles:
+        launch(tile_rows, tile_starts, num_tiles, 0)
+    if ctx.num_decode_rows:
+        launch(ctx.decode_rows, ctx.decode_tokens, ctx.num_decode_rows, 1)
 
 
 DECODE_SPLIT = 128  # keys per split of the split-KV kernel (csrc/attention_mma.cu: DEC_SPLIT)

@@ -32,6 +32,7 @@ LIBRARIES: dict[str, list[str]] = {
     "rope_kv": [],
     "attention_generic": [],
     "diff_attention": [],
+    "diff_attention_mma": [],
     "attention_mma": [],
     "attention_decode_static": [],
     "attention_decode_tma": [],

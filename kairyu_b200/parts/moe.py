@@ -139,7 +139,6 @@ class MixtureOfExperts(FeedForward):
         pairs = tokens * top
         plan = kernels.moe_plan(ids, experts, ws.flat("moe.plan", kernels.moe_plan_size(pairs, experts), torch.int32))
         unit = dict(limit=self.limit, alpha=self.alpha, shift=self.shift)
-        ends = plan["ends"][: self.num_experts]  # where the runs of the experts with weights end
         if kernels.moe_skinny_ok(tokens, self.hidden_size, self.intermediate_size, self.dtype):
             # a decode-sized step: an expert has a handful of pairs and its weights stream once (gate and up with the
             # activation in the epilogue, then down)
@@ -150,6 +149,7 @@ class MixtureOfExperts(FeedForward):
         elif kernels.moe_library_products_ok(self.hidden_size, self.intermediate_size, self.dtype):
             # bfloat16, aligned sizes: the tokens' rows are laid out run by run and the library's grouped
             # product (group sizes read on the device) runs both products; the rows stay in that order
+            ends = plan["ends"][: self.num_experts]  # where the runs of the experts with weights end
             gathered = ws.buffer("moe.gathered", pairs, self.hidden_size, self.dtype)
             kernels.gather_rows(x, plan["token_of"], gathered)
             gate_up = kernels.moe_library_product(gathered, self.w_gate_up, ends)

@@ -113,7 +113,7 @@ def moe_plan(ids, experts, plan):
     return {"sorted": order, "experts": flat, "top": top}
 
 
-def moe_grouped(a, weight, out, plan, *, top, gated, limit=0.0, alpha=1.702):
+def moe_grouped(a, weight, out, plan, *, top, gated, limit=0.0, alpha=1.702, shift=1.0):
     for place, pair in enumerate(plan["sorted"]):
         w = weight[plan["experts"][pair]].float()
         if gated:
@@ -121,7 +121,7 @@ def moe_grouped(a, weight, out, plan, *, top, gated, limit=0.0, alpha=1.702):
             half = both.shape[0] // 2
             g = both[:half].clamp(max=limit)
             u = both[half:].clamp(min=-limit, max=limit)
-            out[place] = (g * torch.sigmoid(alpha * g) * (u + 1.0)).to(out.dtype)
+            out[place] = (g * torch.sigmoid(alpha * g) * (u + shift)).to(out.dtype)
         else:
             out[pair] = w @ a[place].float()
 

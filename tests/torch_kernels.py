@@ -16,8 +16,8 @@ import plain_model
 DECODE_SPLIT = 128
 
 
-def embedding(table, ids, out, flag=None):
-    out.copy_(table[ids.long()].float())
+def embedding(table, ids, out, flag=None, *, scale=1.0):
+    out.copy_(table[ids.long()].float() * scale)
 
 
 def patch_tokens(ids, source, sampled, flag=None):
