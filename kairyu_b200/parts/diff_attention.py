@@ -21,13 +21,14 @@ cache slot another layer of the same geometry wrote earlier in the step (``Layer
 with its own queries, window and constants.  ``keep`` is how many positions the cache slot keeps: at
 least the widest window among the layers that read it (None: all).
 
-Steps: one product for q|k|v, the page write, attention, the output product.  Scores, softmax, the
+Steps: one product for q|k|v, the page write, attention, the output product.  For a few bfloat16 rows the
+two products take the norms around the mixer into their epilogues (``fusable_norm``), as the package's other
+attention does.  Scores, softmax, the
 combination and the head norm are 32-bit in both modes; ``lam`` is computed once, at loading, in 32-bit.
 """
 
 from __future__ import annotations
 
-import math
 from typing import Any, Mapping, Optional
 
 import torch
@@ -130,7 +131,13 @@ class DifferentialAttention(Mixer):
         return (kernels.DIFF_ATTENTION_TILE,) if self._tensor_cores() else ()
 
     # -- compute
-    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView) -> torch.Tensor:
+    def fusable_norm(self, tokens: int) -> bool:
+        """Whether the q|k|v and the output product can take the norms around them into their epilogues."""
+        return kernels.fused_norm_shapes_ok(tokens, self.hidden_size, self.out_size)
+
+    def forward(self, x, ctx: StepContext, cache: CacheView, fold=None):
+        """``x``: rows, or a ``kernels.PreNormed``; ``fold`` (a ``kernels.ResidualNorm``): the output product
+        adds its result to the residual and returns the ``PreNormed`` for the next norm."""
         tokens = x.shape[0]
         ws = ctx.workspace
         packed = ws.buffer("diff.packed", tokens, self.packed_width, self.dtype)
@@ -152,6 +159,9 @@ class DifferentialAttention(Mixer):
             kernels.diff_attention_generic(
                 packed, mixed, cache.k, cache.v, positions=ctx.positions, row_ids=ctx.row_ids, block_table=block_table, **constants
             )
+        if fold is not None:
+            kernels.linear(mixed, self.w_o, None, None, fold=fold)
+            return fold.result()
         out = ws.buffer("diff.out", tokens, self.hidden_size, self.dtype)
         kernels.linear(mixed, self.w_o, None, out)
         return out
