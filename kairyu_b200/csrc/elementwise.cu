@@ -75,26 +75,6 @@ __device__ __forceinline__ float unary_activation(float x, int kind) {
     return x / (1.0f + expf(-x));
 }
 
-template <typename T>
-__global__ void __launch_bounds__(256) activation_kernel(const T* __restrict__ x, T* __restrict__ y, size_t total, int kind) {
-    pdl_wait();
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
-        y[i] = from_float<T>(unary_activation(to_float(x[i]), kind));
-}
-
-KB_EXPORT int kb_activation(const void* x, void* y, int is_bf16, long long total, int kind, cudaStream_t stream) {
-    if (total == 0) return 0;
-    if (!x || !y) return KB_ERR_NULL;
-    if (kind < 0 || kind > 2 || total < 0) return KB_ERR_BAD_ARG;
-    long long blocks = (total + 255) / 256;
-    if (blocks > 148 * 16) blocks = 148 * 16;
-    if (is_bf16)
-        kb_launch(activation_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, stream, (const __nv_bfloat16*)x, (__nv_bfloat16*)y, (size_t)total, kind);
-    else
-        kb_launch(activation_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, stream, (const float*)x, (float*)y, (size_t)total, kind);
-    return kb_launch_result();
-}
-
 // ------------------------------------------------------------------ tokens that are still on the device
 // ids[t] = sampled[source[t]] where source[t] >= 0: the token a step is fed may be the one the
 // step before it has just chosen, which the host has not seen yet
@@ -190,6 +170,58 @@ struct Vec4<__nv_bfloat16> {
         *reinterpret_cast<uint2*>(p) = r;
     }
 };
+
+// ---- the activation kernels (unary_activation is defined with the feed-forward's activations above)
+template <typename T>
+__global__ void __launch_bounds__(256) activation_kernel(const T* __restrict__ x, T* __restrict__ y, size_t total, int kind) {
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+        y[i] = from_float<T>(unary_activation(to_float(x[i]), kind));
+}
+
+// eight elements a thread a turn (two chunks of four), for totals that are a multiple of four on 16-byte aligned rows
+template <typename T>
+__global__ void __launch_bounds__(256) activation_vec_kernel(const T* __restrict__ x, T* __restrict__ y, size_t chunks, int kind) {
+    pdl_wait();
+    const size_t step = (size_t)gridDim.x * blockDim.x;
+    for (size_t c = (size_t)blockIdx.x * blockDim.x + threadIdx.x; c < chunks; c += 2 * step) {
+        float a[4], b[4];
+        const bool second = c + step < chunks;
+        Vec4<T>::load(x + 4 * c, a);
+        if (second) Vec4<T>::load(x + 4 * (c + step), b);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) a[e] = unary_activation(a[e], kind);
+        Vec4<T>::store(y + 4 * c, a);
+        if (second) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) b[e] = unary_activation(b[e], kind);
+            Vec4<T>::store(y + 4 * (c + step), b);
+        }
+    }
+}
+
+KB_EXPORT int kb_activation(const void* x, void* y, int is_bf16, long long total, int kind, cudaStream_t stream) {
+    if (total == 0) return 0;
+    if (!x || !y) return KB_ERR_NULL;
+    if (kind < 0 || kind > 2 || total < 0) return KB_ERR_BAD_ARG;
+    if (total % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)y % 16 == 0) {
+        const long long chunks = total / 4;
+        long long blocks = (chunks + 511) / 512;
+        if (blocks > 148 * 8) blocks = 148 * 8;
+        if (is_bf16)
+            kb_launch(activation_vec_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, stream, (const __nv_bfloat16*)x, (__nv_bfloat16*)y, (size_t)chunks, kind);
+        else
+            kb_launch(activation_vec_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, stream, (const float*)x, (float*)y, (size_t)chunks, kind);
+        return kb_launch_result();
+    }
+    long long blocks = (total + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (is_bf16)
+        kb_launch(activation_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, stream, (const __nv_bfloat16*)x, (__nv_bfloat16*)y, (size_t)total, kind);
+    else
+        kb_launch(activation_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, stream, (const float*)x, (float*)y, (size_t)total, kind);
+    return kb_launch_result();
+}
 
 // The sum of a row's squares is added in one order whatever the block's size: chunk by chunk (four
 // elements each), then group g = 0..G-1 adds the partial sums of chunks g, g + G, g + 2G, g + 3G in that
