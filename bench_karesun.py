@@ -26,11 +26,11 @@ WINDOW = 1024
 
 
 def karesun_config(size: dict) -> dict:
-    mixer = {"heads": size["heads"], "kv_heads": size["kv_heads"], "dim": 64, "vdim": 128, "scale": 64 ** -0.5, "softcap": 30.0,
-             "diff": 0.5, "mask": {"size": WINDOW}}
+    mixer = {"heads": size["heads"], "kv_heads": size["kv_heads"], "dim": 64, "vdim": 128, "scale": 64 ** -0.5, "softcap": 50.0,
+             "diff": 0.4, "mask": {"size": WINDOW}}
     dense = {"kind": "dense", "ff": size["top"] * size["ff"]}
     mixture = {"kind": "moe", "expert": {"ff": size["ff"]},
-               "router": {"experts": size["experts"], "identity": size["identity"], "top": size["top"], "scale": 1.5, "groups": {"count": 4, "keep": 2}}}
+               "router": {"experts": size["experts"], "identity": size["identity"], "top": size["top"], "scale": 2.0, "groups": {"count": 4, "keep": 2}}}
     layers = []
     for index in range(LAYERS):
         if index % 2 == 0:

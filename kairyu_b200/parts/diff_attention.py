@@ -23,8 +23,8 @@ least the widest window among the layers that read it (None: all).
 
 Steps: one product for q|k|v, the page write, attention, the output product.  For a few bfloat16 rows the
 two products take the norms around the mixer into their epilogues (``fusable_norm``), as the package's other
-attention does.  Scores, softmax, the
-combination and the head norm are 32-bit in both modes; ``lam`` is computed once, at loading, in 32-bit.
+attention does.  Scores, softmax, the combination and the head norm are 32-bit in both modes; ``lam`` is
+computed once, at loading, in 32-bit.
 """
 
 from __future__ import annotations
@@ -86,8 +86,7 @@ class DifferentialAttention(Mixer):
         self.packed_width = self.q_size + (self.k_size + self.v_size if own_kv else 0)
         self.w_in: Optional[torch.Tensor] = None  # [q | k | v rows, hidden]; q rows only without own_kv
         self.w_o: Optional[torch.Tensor] = None
-        self.lam: float = self.lam_init
-        self._lam_vectors: Optional[torch.Tensor] = None
+        self.lam: float = self.lam_init  # until the four vectors are loaded
 
     # -- weights
     def tensor_specs(self) -> list[TensorSpec]:
@@ -108,8 +107,7 @@ class DifferentialAttention(Mixer):
         self.w_in = torch.cat(rows, dim=0).contiguous()
         self.w_o = tensors[f"{p}.o"].contiguous()
         lq1, lk1, lq2, lk2 = (tensors[f"{p}.{name}"].float() for name in ("lq1", "lk1", "lq2", "lk2"))
-        self._lam_vectors = torch.stack([lq1, lk1, lq2, lk2])
-        if not self._lam_vectors.is_meta:
+        if not lq1.is_meta:
             # one number a layer, from weights alone: formed once, in 32-bit
             first = torch.exp((lq1 * lk1).sum())
             second = torch.exp((lq2 * lk2).sum())
